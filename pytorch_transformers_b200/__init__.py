@@ -1,12 +1,12 @@
 """pytorch_transformers_b200: a small model library with generation of its own for one NVIDIA
 B200 (sm_100a): typed configuration and registry, safetensors weights, models put together from
 parts, a paged cache, one step function, a generation loop, sampling, trace replay.
-Architectures built: Falcon, Pafevik, Zalunex."""
+Architectures built: Falcon, Pafevik, Zalunex, Pogezen."""
 from . import models  # noqa: F401  (registers the built-in architectures)
 from .cache.paged import Cache
 from .cache.pool import CacheError, CacheFull
 from .config import (AutoConfig, ConfigError, FalconConfig, GenerationConfig, ModelConfig, PafevikConfig,
-                     ZalunexConfig, register_architecture)
+                     PogezenConfig, ZalunexConfig, register_architecture)
 from .engine.batch import StepError
 from .engine.model import CausalLM
 from .modeling import AutoModelForCausalLM, FalconForCausalLM, GenerateOutput, PreTrainedCausalLM

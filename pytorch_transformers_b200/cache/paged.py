@@ -5,7 +5,8 @@ Storage groups. Cache entries (one per schedule entry that writes a cache) with 
 (kind, K/V heads, head size, window) share a group; each group has its own page pool and its
 own device storage ``k, v: [entries, pages, kv_heads, PAGE, head_dim]``. A ``full`` group keeps
 every key and value of a sequence; a ``window`` group gives pages back once every position in
-them is older than the window (positions left of ``length - window`` are never read again).
+them is older than the window (positions left of ``length - window`` are never read again; with
+``keep_first`` the pages of a sequence's first positions are held as long as the sequence lives).
 The reference's analogues are StaticCache (src/transformers/cache_utils.py:1058-1230: storage
 allocated once, written in place), HybridCache (:1550-1743: per-layer kinds with their own
 shapes) and MambaCache (:1746-1859: fixed-size state per batch row, reset in place).
@@ -153,10 +154,11 @@ class Cache:
             first_needed = CACHE_KINDS[g.need.kind](g.need, rec.length)
             if first_needed >= PAGE:
                 dead = first_needed // PAGE
-                gone = [p for p in rec.pages[gi][:dead] if p >= 0]
+                kept = (g.need.keep_first + PAGE - 1) // PAGE     # pages of positions that stay readable for good
+                gone = [p for p in rec.pages[gi][kept:dead] if p >= 0]
                 if gone:
                     g.pool.give_back(gone)
-                    for i in range(dead):
+                    for i in range(kept, dead):
                         rec.pages[gi][i] = -1
 
     def close(self, slot: int) -> None:

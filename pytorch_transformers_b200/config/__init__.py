@@ -3,4 +3,5 @@ from .falcon import FalconConfig
 from .generation import GenerationConfig
 from .pafevik import PafevikConfig
 from .zalunex import ZalunexConfig
+from .pogezen import PogezenConfig
 from .registry import AutoConfig, Architecture, lookup, lookup_config, register_architecture, registered

@@ -16,6 +16,9 @@ constexpr int THREADS = 128;  // 8 threads per query row
 constexpr int MAX_D = 256;    // head sizes up to this
 constexpr int DPT = MAX_D / 8;
 
+// a float as the tensors' type holds it
+template <typename T> __device__ __forceinline__ float round_store(float v) { return to_f(from_f<T>(v)); }
+
 // ------------------------------------------------------------------------------------------------
 // Fused projection [n_tokens, kv_heads * (q_per_kv + 2) * head_dim], rows grouped per K/V head as
 // (q_per_kv query heads, K, V), to: q_out [n_tokens, heads, head_dim] (query head = group *
@@ -143,7 +146,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          const int* __restrict__ tile_q0, const float* __restrict__ alibi_slopes, int heads,
                          int kv_heads, int head_dim, float scale, int window, int v_dim,
                          const float* __restrict__ sinks, const T* __restrict__ gate, int gate_stride, float out_scale,
-                         int out_stride) {
+                         int out_stride, int keep_first, float* __restrict__ out_wide) {
   extern __shared__ float smem[];
   const int wide = max(head_dim, v_dim);
   float* qs = smem;                                 // [BQ][head_dim]
@@ -156,6 +159,9 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
   const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
   const int rows = min(BQ, n_new - q0);
   const int g = h / (heads / kv_heads);
+  // with out_wide the grid's third dimension names the K/V head whose values this block reads (the scores are
+  // head h's own): every head's weights meet every K/V head's values, for a mixing of the heads' weights afterwards
+  const int gv = out_wide ? int(blockIdx.z) : g;
   const int tid = threadIdx.x;
   const int r = tid / 8, c = tid % 8;
   const int my_pos = (r < rows) ? past + q0 + r : -1;  // -1: no key is visible, nothing is stored
@@ -176,12 +182,15 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
   if (window > 0) kb_lo = max(0, first_pos - window + 1) / PTB_PAGE;
   const int kb_hi = last_pos / PTB_PAGE;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
+  // the first keep_first positions stay visible left of the window: their pages are walked first
+  const int kept_pages = (window > 0 && keep_first > 0) ? min((keep_first + PTB_PAGE - 1) / PTB_PAGE, kb_lo) : 0;
 
-  for (int kb = kb_lo; kb <= kb_hi; ++kb) {
+  for (int kb = (kept_pages > 0 ? 0 : kb_lo); kb <= kb_hi; ++kb) {
+    if (kb == kept_pages && kb < kb_lo) kb = kb_lo;
     const int page = pages[kb];
     const int valid = min(PTB_PAGE, last_pos + 1 - kb * PTB_PAGE);  // keys of this block that exist
     const T* kp = k_pool + kv_offset(page, g, 0, kv_heads, head_dim);
-    const T* vp = v_pool + kv_offset(page, g, 0, kv_heads, v_dim);
+    const T* vp = v_pool + kv_offset(page, gv, 0, kv_heads, v_dim);
     __syncthreads();  // previous block's V and ps are no longer read
     for (int i = tid; i < PTB_PAGE * head_dim; i += THREADS) {
       const int j = i / head_dim, e = i % head_dim;
@@ -200,7 +209,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
       const float* kr = kv + j * kstride;
       for (int e = 0; e < head_dim; ++e) dot = fmaf(qr[e], kr[e], dot);
       bool visible = key_pos <= my_pos;
-      if (window > 0) visible = visible && (key_pos > my_pos - window);
+      if (window > 0) visible = visible && (key_pos > my_pos - window || key_pos < keep_first);
       float sc = -INFINITY;
       if (visible) {
         if (alibi_slopes) dot += alibi_bias(slope, key_pos);
@@ -258,6 +267,16 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
     }
     float inv = (l_run > 0.f ? 1.f / l_run : 0.f) * keep * out_scale;
     if (gate) inv *= 1.f / (1.f + expf(-to_f(gate[size_t(start + q0 + r) * gate_stride + h])));
+    if (out_wide) {
+      // float32 [token][head][K/V head][v_dim]
+      float* o = out_wide + ((size_t(start + q0 + r) * heads + h) * kv_heads + gv) * v_dim;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        const int e = c + 8 * i;
+        if (e < v_dim) o[e] = acc[i] * inv;
+      }
+      return;
+    }
     T* o = out + size_t(start + q0 + r) * out_stride + size_t(h) * v_dim;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -267,11 +286,88 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Separate projections q | k | v side by side in a row of `proj` (rows `stride` apart), an optional bias on all of
+// them (float32, added here in float32), then for every query and key head: rotation of the first 2 rot_pairs
+// entries (pairs (i, i + rot_pairs); the table holds cos and sin of the token's angles, with whatever factor the
+// position part puts on them), then, with `unit_norm`, division by the head's root mean square (eps inside the
+// root, no gain). Values: v <- (1 - lam) v + lam v_first with the values of the same token that an earlier layer
+// kept (`v_first`, rows v_first_stride apart; lam one float32 on the device); `v_keep` receives this layer's own
+// values (with bias, before any mixing) for later layers. Keys and values go into the paged pools at the tokens'
+// positions, queries to q_out [tokens, heads, dim]. One block per token, a warp per head.
+template <typename T>
+__global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, const float* __restrict__ bias,
+                                       T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool, StepBatch sb,
+                                       const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int rot_pairs,
+                                       int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm,
+                                       const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ lam,
+                                       T* __restrict__ v_keep, int write_cache) {
+  extern __shared__ float rows[];   // a row of `dim` floats per warp
+  const int t = blockIdx.x;
+  const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
+  const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE], in_page = pos % PTB_PAGE;
+  const T* row = proj + size_t(t) * stride;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, n_warps = blockDim.x / 32;
+  float* buf = rows + size_t(warp) * dim;
+  for (int hh = warp; hh < heads + kv_heads; hh += n_warps) {
+    const bool is_q = hh < heads;
+    if (!is_q && !write_cache) continue;
+    const T* src = row + size_t(hh) * dim;
+    const float* bsrc = bias ? bias + size_t(hh) * dim : nullptr;
+    T* dst = is_q ? q_out + (size_t(t) * heads + hh) * dim : k_pool + kv_offset(page, hh - heads, in_page, kv_heads, dim);
+    for (int e = lane; e < dim; e += 32) buf[e] = to_f(src[e]) + (bsrc ? bsrc[e] : 0.f);
+    __syncwarp();
+    for (int i = lane; i < rot_pairs; i += 32) {
+      const float c = rope_cos[size_t(t) * rot_pairs + i], s = rope_sin[size_t(t) * rot_pairs + i];
+      float a, b;
+      rotate_pair(buf[i], buf[i + rot_pairs], c, s, a, b);
+      buf[i] = a;
+      buf[i + rot_pairs] = b;
+    }
+    __syncwarp();
+    float rstd = 1.f;
+    if (unit_norm) {
+      float ss = 0.f;
+      for (int e = lane; e < dim; e += 32) ss = fmaf(buf[e], buf[e], ss);
+      rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+    }
+    for (int e = lane; e < dim; e += 32) dst[e] = from_f<T>(buf[e] * rstd);
+    __syncwarp();
+  }
+  const T* vsrc = row + size_t(heads + kv_heads) * dim;
+  const float* vb = bias ? bias + size_t(heads + kv_heads) * dim : nullptr;
+  const float l = (v_first != nullptr) ? lam[0] : 0.f;
+  for (int i = threadIdx.x; i < kv_heads * v_dim; i += blockDim.x) {
+    const int g = i / v_dim, e = i % v_dim;
+    float v = to_f(vsrc[i]) + (vb ? vb[i] : 0.f);
+    if (v_keep) v_keep[size_t(t) * kv_heads * v_dim + i] = from_f<T>(v);
+    if (v_first != nullptr) v = (1.f - l) * round_store<T>(v) + l * to_f(v_first[size_t(t) * v_first_stride + i]);
+    if (write_cache) v_pool[kv_offset(page, g, in_page, kv_heads, v_dim) + e] = from_f<T>(v);
+  }
+}
+
+// out[t][h][:] = sum_g talk[h][g] * wide[t][g][kv head of h][:]: the heads' softmax weights mixed after the softmax,
+// applied to head h's own values, written as the sum over g of what every head's weights gave on those values.
+// wide float32 [tokens][heads][kv_heads][v_dim]; talk float32 [heads][heads]; ascending g, float32.
+template <typename T>
+__global__ void talk_mix_kernel(const float* __restrict__ wide, const float* __restrict__ talk, T* __restrict__ out,
+                                int out_stride, long long total, int heads, int kv_heads, int v_dim) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int e = int(i % v_dim), h = int((i / v_dim) % heads);
+  const long long t = i / (v_dim * (long long)heads);
+  const int c = h / (heads / kv_heads);
+  const float* src = wide + (size_t(t) * heads * kv_heads + c) * v_dim + e;
+  float acc = 0.f;
+  for (int g = 0; g < heads; ++g) acc = fmaf(talk[size_t(h) * heads + g], src[size_t(g) * kv_heads * v_dim], acc);
+  out[size_t(t) * out_stride + size_t(h) * v_dim + e] = from_f<T>(acc);
+}
+
 template <typename T>
 int launch_attention(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch& sb,
                      const int* tile_seq, const int* tile_q0, int n_tiles, const float* slopes, int heads,
                      int kv_heads, int head_dim, float scale, int window, int v_dim, const float* sinks, const void* gate,
-                     int gate_stride, float out_scale, int out_stride, cudaStream_t stream) {
+                     int gate_stride, float out_scale, int out_stride, int keep_first, float* out_wide, cudaStream_t stream) {
   const int wide = head_dim > v_dim ? head_dim : v_dim;
   const size_t smem = sizeof(float) * (size_t(BQ) * head_dim + size_t(PTB_PAGE) * (wide + 1) + BQ * PTB_PAGE);
   static size_t configured = 48 * 1024;  // per element type: raised when a larger head size first comes
@@ -281,11 +377,11 @@ int launch_attention(const void* q, const void* k_pool, const void* v_pool, void
       return PTB_ERR_LAUNCH;
     configured = smem;
   }
-  dim3 grid(n_tiles, heads);
+  dim3 grid(n_tiles, heads, out_wide ? kv_heads : 1);
   attention_generic_kernel<T><<<grid, THREADS, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool,
                                                                (T*)out, sb, tile_seq, tile_q0, slopes, heads, kv_heads,
                                                                head_dim, scale, window, v_dim, sinks, (const T*)gate,
-                                                               gate_stride, out_scale, out_stride);
+                                                               gate_stride, out_scale, out_stride, keep_first, out_wide);
   return launch_status();
 }
 
@@ -337,21 +433,68 @@ PTB_API int ptb_attention_generic(int dtype, const void* q, const void* k_pool, 
                                   const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
                                   const float* alibi_slopes, int heads, int kv_heads, int head_dim, float scale,
                                   int window, int v_dim, const float* sinks, const void* gate, int gate_stride,
-                                  float out_scale, int out_stride, cudaStream_t stream) {
+                                  float out_scale, int out_stride, int keep_first, float* out_wide, cudaStream_t stream) {
+  // keep_first: with a window, the sequence's first keep_first positions stay visible too. out_wide (float32
+  // [tokens][heads][kv_heads][v_dim], or null): every head's weights on every K/V head's values instead of `out`.
   if (n_tiles <= 0) return PTB_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim <= 0 || head_dim > MAX_D || heads > 65535 ||
-      v_dim <= 0 || v_dim > MAX_D || out_stride < heads * v_dim)
+      v_dim <= 0 || v_dim > MAX_D || (out_wide == nullptr && out_stride < heads * v_dim) || keep_first < 0 ||
+      (out_wide != nullptr && kv_heads > 65535))
     return PTB_ERR_SIZE;
   if (dtype == PTB_F32)
     return launch_attention<float>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
                                    kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride, out_scale, out_stride,
-                                   stream);
+                                   keep_first, out_wide, stream);
   if (dtype == PTB_BF16)
     return launch_attention<__nv_bfloat16>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, alibi_slopes,
                                            heads, kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride,
-                                           out_scale, out_stride, stream);
+                                           out_scale, out_stride, keep_first, out_wide, stream);
   return PTB_ERR_DTYPE;
 }
 
 // rows of a tile of the general kernel, for the host that builds the tile lists
 PTB_API int ptb_attention_generic_tile_rows() { return BQ; }
+
+// bias: float32 [(heads + kv_heads) dim + kv_heads v_dim] or null; rope_cos / rope_sin: float32 [tokens, rot_pairs] or null;
+// v_first (rows v_first_stride apart), lam, v_keep [tokens, kv_heads v_dim]: null where not used.
+PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const float* bias, void* q_out, void* k_pool,
+                                void* v_pool, const StepBatch* sb, const float* rope_cos, const float* rope_sin, int rot_pairs,
+                                int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm, const void* v_first,
+                                int v_first_stride, const float* lam, void* v_keep, int write_cache, cudaStream_t stream) {
+  if (sb->n_tokens <= 0) return PTB_OK;
+  if (heads <= 0 || kv_heads <= 0 || dim <= 0 || v_dim <= 0 || stride < (heads + kv_heads) * dim + kv_heads * v_dim ||
+      rot_pairs < 0 || 2 * rot_pairs > dim || (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) ||
+      (v_first != nullptr && lam == nullptr) || dim > 4096)
+    return PTB_ERR_SIZE;
+  const int threads = 256;
+  const size_t smem = size_t(threads / 32) * dim * sizeof(float);
+  if (smem > 48 * 1024) return PTB_ERR_SIZE;
+  if (dtype == PTB_F32)
+    rope_norm_store_kernel<float><<<sb->n_tokens, threads, smem, stream>>>(
+        (const float*)proj, stride, bias, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, rope_cos, rope_sin, rot_pairs,
+        heads, kv_heads, dim, v_dim, eps, unit_norm, (const float*)v_first, v_first_stride, lam, (float*)v_keep, write_cache);
+  else if (dtype == PTB_BF16)
+    rope_norm_store_kernel<__nv_bfloat16><<<sb->n_tokens, threads, smem, stream>>>(
+        (const __nv_bfloat16*)proj, stride, bias, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
+        rope_cos, rope_sin, rot_pairs, heads, kv_heads, dim, v_dim, eps, unit_norm, (const __nv_bfloat16*)v_first,
+        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
+PTB_API int ptb_talk_mix(int dtype, const float* wide, const float* talk, void* out, int out_stride, int n_tokens, int heads,
+                         int kv_heads, int v_dim, cudaStream_t stream) {
+  if (n_tokens <= 0) return PTB_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || v_dim <= 0 || out_stride < heads * v_dim) return PTB_ERR_SIZE;
+  const long long total = (long long)n_tokens * heads * v_dim;
+  const unsigned blocks = unsigned((total + 255) / 256);
+  if (dtype == PTB_F32)
+    talk_mix_kernel<float><<<blocks, 256, 0, stream>>>(wide, talk, (float*)out, out_stride, total, heads, kv_heads, v_dim);
+  else if (dtype == PTB_BF16)
+    talk_mix_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(wide, talk, (__nv_bfloat16*)out, out_stride, total, heads,
+                                                               kv_heads, v_dim);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}

@@ -115,6 +115,7 @@ class StepContext:
         self.side_stream = None     # set by the engine for steps of a few tokens (see parts/block.py)
         self.next_block = None      # set by the engine before every block: the block that runs after it
         self._rope: dict = {}
+        self.shared: dict = {}      # what one block leaves for later blocks of the same step (a first layer's values, say)
         self.keep_alive: list = []  # tensors that must outlive the step's last kernel on another stream
         self.slots = [int(s) for s in slots]
         self.n_seqs = len(slots)
@@ -260,7 +261,17 @@ class StepContext:
         """Forget what an earlier forward pass over this step computed (a step that is captured as a
         graph runs once plainly and once under capture: the capture must contain every kernel)."""
         self._rope = {}
+        self.shared = {}
         self.keep_alive = []
+
+    def state_of(self, entry, numel: int):
+        """[slots, numel] float32: the running mixer's own stretch of the per-sequence state of ``entry``'s cache entry
+        (it begins at ``entry.state_offset``)."""
+        state = self.cache.entry_state(entry.cache_entry)
+        off = int(getattr(entry, "state_offset", 0))
+        if state is None or off + numel > state.shape[1]:
+            raise StepError(f"cache entry {entry.cache_entry} has no per-sequence state of {off + numel} values")
+        return state[:, off:off + numel]
 
     def rope(self, position_part):
         """(cos, sin) tables of this step's tokens for a rotary position part, computed once per step
@@ -271,7 +282,12 @@ class StepContext:
             return None
         key = getattr(position_part, "rotation_key", None) or id(position_part)
         if key not in self._rope:
-            self._rope[key] = K.rope_table(self.dev["tok_pos"], inv_freq)
+            cos, sin = K.rope_table(self.dev["tok_pos"], inv_freq)
+            factor = float(getattr(position_part, "table_scale", 1.0))   # a factor on both tables (YaRN)
+            if factor != 1.0:
+                K.scale_(cos, factor)
+                K.scale_(sin, factor)
+            self._rope[key] = (cos, sin)
         return self._rope[key]
 
     def plan(self, plan_key: str) -> StepPlan:

@@ -382,6 +382,8 @@ class CausalLM:
             x = k.embed_sum(ctx.dev["tokens"], ctx.dev["tok_pos"], self.embedding, self.position_table, self.status)
         else:
             x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
+        if self.spec.stream_float32 and x.dtype != torch.float32 and self.embedding_norm is None:
+            x = k.to_float(x)       # widened before the scale: the stream's first value is formed in float32
         if self.spec.embedding_scale != 1.0:
             k.scale_(x, self.spec.embedding_scale)
         if self.embedding_norm is not None:

@@ -16,7 +16,7 @@ from . import native
 
 PAGE = 64  # tokens of a cache page (PTB_PAGE in csrc/common.cuh)
 # names (src/transformers/activations.py:200-228) -> the codes of csrc/common.cuh, the kernels' one table
-ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3}
+ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3, "relu2": 4}   # relu2: relu(x)^2
 NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
 _ERRORS = {1: "unknown dtype code", 2: "a size that the kernel does not take", 3: "the CUDA launch failed",
            4: "a pointer or row size is not aligned as the kernel needs"}
@@ -98,7 +98,9 @@ def lib():
                      "ptb_linear_attention_chunks", "ptb_linear_attention_chunks_supports", "ptb_norm_gate",
                      "ptb_qk_norm_store", "ptb_post_norm_add", "ptb_embed_sum", "ptb_softcap", "ptb_glu_clamp",
                      "ptb_attention_mma_gated", "ptb_linear_attention_chunk_join", "ptb_linear_attention_mma_supports",
-                     "ptb_linear_attention_chunks_mma", "ptb_linear_attention_token"):
+                     "ptb_linear_attention_chunks_mma", "ptb_linear_attention_token", "ptb_dyt", "ptb_mlstm_gates",
+                     "ptb_mlstm_scan", "ptb_mlstm_max_dim", "ptb_mlstm_state_floats", "ptb_head_norm_gate",
+                     "ptb_rope_norm_store", "ptb_talk_mix"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -241,14 +243,27 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                       tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
                       slopes: Optional[torch.Tensor], kv_heads: int, scale: float, window: int = 0,
                       sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, keep_first: int = 0, wide: bool = False) -> torch.Tensor:
     """Causal attention of the step's tokens over the paged cache; returns [tokens, heads * v_dim] (v_dim is
     the V pool's row size). ``sinks`` [heads] float32: one more term exp(sink) in every row's softmax denominator,
     for which nothing is read. ``gate`` [tokens, heads] (a view whose rows may be wider apart): each head's
-    output times sigmoid(gate). ``out``: a [tokens, heads * v_dim] view (rows may be wider apart) to write into."""
+    output times sigmoid(gate). ``out``: a [tokens, heads * v_dim] view (rows may be wider apart) to write into.
+    ``keep_first``: with a window, a sequence's first ``keep_first`` positions stay visible as well. ``wide``: returns
+    float32 [tokens, heads, kv_heads, v_dim] instead, every head's softmax weights applied to every K/V head's values
+    (what ``talk_mix`` sums when the heads' weights are mixed after the softmax)."""
     _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, sinks)
     n, heads, head_dim = q.shape
     v_dim = v_pool.shape[-1]
+    if wide:
+        if gate is not None or sinks is not None or out is not None or out_scale != 1.0:
+            raise KernelError("attention_generic: the wide form takes no sink, gate, factor or output view")
+        res = torch.empty((n, heads, kv_heads, v_dim), dtype=torch.float32, device=q.device)
+        _check(lib().ptb_attention_generic(_dtype_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), None,
+                                           ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                           heads, kv_heads, head_dim, ctypes.c_float(scale), window, v_dim, None,
+                                           None, 0, ctypes.c_float(1.0), 0, int(keep_first), _ptr(res), _stream(q)),
+               "attention_generic (wide)")
+        return res
     if out is None:
         out = torch.empty((n, heads * v_dim), dtype=q.dtype, device=q.device)
     _check_rows(out, (n, heads * v_dim), q.dtype, "attention_generic: out")
@@ -258,8 +273,52 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                        ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
                                        heads, kv_heads, head_dim, ctypes.c_float(scale), window, v_dim, _ptr(sinks),
                                        _ptr(gate), 0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
-                                       out.stride(0), _stream(q)),
+                                       out.stride(0), int(keep_first), None, _stream(q)),
            "attention_generic")
+    return out
+
+
+def rope_norm_store(proj: torch.Tensor, bias: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor,
+                    batch: StepBatchC, rope, heads: int, kv_heads: int, dim: int, v_dim: int, eps: float,
+                    unit_norm: bool = True, v_first: Optional[torch.Tensor] = None, lam: Optional[torch.Tensor] = None,
+                    keep_values: bool = False, write_cache: bool = True):
+    """``proj`` [tokens, >= (heads + kv_heads) dim + kv_heads v_dim] holds q, k, v side by side (rows may lie wider
+    apart); ``bias`` (float32, as long) is added in float32. Queries and keys: rotation of a head's first entries by
+    ``rope`` = (cos, sin) tables [tokens, pairs] (None: none), then, with ``unit_norm``, division by the head's root mean
+    square. Values: ``(1 - lam) v + lam v_first`` where ``v_first`` [tokens, kv_heads v_dim] is given (``lam``: one
+    float32 on the device). Keys and values go into the paged pools. Returns q [tokens, heads, dim], and with
+    ``keep_values`` also this layer's own values [tokens, kv_heads v_dim] as they were before any mixing."""
+    _need_cuda(k_pool, v_pool, bias, lam)
+    _check_rows(proj, proj.shape, proj.dtype, "rope_norm_store: proj")
+    n = proj.shape[0]
+    q = torch.empty((n, heads, dim), dtype=proj.dtype, device=proj.device)
+    kept = torch.empty((n, kv_heads * v_dim), dtype=proj.dtype, device=proj.device) if keep_values else None
+    cos, sin = rope if rope is not None else (None, None)
+    pairs = 0 if cos is None else cos.shape[1]
+    if v_first is not None:
+        _check_rows(v_first, (n, kv_heads * v_dim), proj.dtype, "rope_norm_store: v_first")
+        if lam is None or lam.dtype != torch.float32:
+            raise KernelError("rope_norm_store: the mixing weight is one float32 on the device")
+    _check(lib().ptb_rope_norm_store(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(bias), _ptr(q), _ptr(k_pool),
+                                     _ptr(v_pool), ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, dim,
+                                     v_dim, ctypes.c_float(eps), 1 if unit_norm else 0, _ptr(v_first),
+                                     0 if v_first is None else v_first.stride(0), _ptr(lam if v_first is not None else None),
+                                     _ptr(kept), 1 if write_cache else 0, _stream(proj)), "rope_norm_store")
+    return (q, kept) if keep_values else q
+
+
+def talk_mix(wide: torch.Tensor, talk: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h] = sum_g talk[h, g] * wide[t, g, K/V head of h]: ``wide`` float32 [tokens, heads, kv_heads, v_dim] from
+    ``attention_generic(wide=True)``, ``talk`` float32 [heads, heads]. Returns [tokens, heads * v_dim] of ``out_dtype``."""
+    _need_cuda(wide, talk)
+    n, heads, kv_heads, v_dim = wide.shape
+    if wide.dtype != torch.float32 or talk.dtype != torch.float32 or tuple(talk.shape) != (heads, heads):
+        raise KernelError("talk_mix takes float32 results [tokens, heads, kv_heads, v_dim] and a float32 matrix [heads, heads]")
+    if out is None:
+        out = torch.empty((n, heads * v_dim), dtype=out_dtype, device=wide.device)
+    _check_rows(out, (n, heads * v_dim), out_dtype, "talk_mix: out")
+    _check(lib().ptb_talk_mix(_dtype_code(out), _ptr(wide), _ptr(talk), _ptr(out), out.stride(0), n, heads, kv_heads, v_dim,
+                              _stream(wide)), "talk_mix")
     return out
 
 
@@ -1140,4 +1199,85 @@ def glu_clamp(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor
     out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(lib().ptb_glu_clamp(_dtype_code(gate_up), _ptr(gate_up), _ptr(out), rows, two_f // 2, ctypes.c_float(limit),
                                ctypes.c_float(alpha), _stream(gate_up)), "glu_clamp")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# The Dynamic Tanh norm with the short convolution on a mixer's input; the matrix memory with exponential gates
+DYT_MAX_TAPS = 8
+
+
+def dyt(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+        conv: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+        batch: Optional[StepBatchC] = None, single_tokens: bool = False) -> torch.Tensor:
+    """h = tanh(alpha x) * weight + bias, elementwise in float32 (``alpha``: one float32 on the device), written in
+    ``out_dtype``. With ``conv`` (float32 [width, taps]) the result is h_t + sum_j conv[:, j] h_(t - taps + 1 + j) over
+    each sequence's tokens; the last ``taps - 1`` rows of h per sequence are read from and left in ``state``
+    [slots, >= (taps - 1) width] (float32; rows may lie wider apart)."""
+    _need_cuda(x, alpha, weight, bias, conv, slots)
+    n, width = x.shape
+    if alpha.dtype != torch.float32 or alpha.numel() != 1 or weight.dtype != torch.float32 or weight.numel() != width:
+        raise KernelError("dyt: alpha is one float32, the weight float32 [width]")
+    y = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    taps = 0
+    if conv is not None:
+        taps = conv.shape[1]
+        if conv.dtype != torch.float32 or conv.shape[0] != width or not (1 <= taps <= DYT_MAX_TAPS) or batch is None:
+            raise KernelError(f"dyt: the convolution is float32 [width, 1..{DYT_MAX_TAPS} taps] and needs the step's batch")
+        if taps > 1 and (state is None or state.dtype != torch.float32 or state.shape[1] < (taps - 1) * width
+                         or state.stride(1) != 1):
+            raise KernelError("dyt: the convolution's state is float32 [slots, >= (taps - 1) * width]")
+    _check(lib().ptb_dyt(_dtype_code(x), _ptr(x), _ptr(alpha), _ptr(weight), _ptr(bias), _dtype_code(y), _ptr(y), n, width,
+                         _ptr(conv), _ptr(state if taps > 1 else None), 0 if state is None or taps <= 1 else state.stride(0),
+                         _ptr(slots), ctypes.byref(batch) if batch is not None else None, taps, 1 if single_tokens else 0,
+                         _stream(x)), "dyt")
+    return y
+
+
+MLSTM_MAX_DIM = 256   # ptb_mlstm_max_dim()
+
+
+def mlstm_state_floats(heads: int, dim: int, v_dim: int) -> int:
+    """float32 values of one sequence's state: S, and a copy of n and m for every stretch of 32 value columns."""
+    return heads * (dim * v_dim + ((v_dim + 31) // 32) * (dim + 1))
+
+
+def mlstm(proj: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+          state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, heads: int, dim: int, v_dim: int,
+          q_scale: float) -> torch.Tensor:
+    """The matrix memory with exponential gates over the step's tokens, continuing and leaving each sequence's state.
+    ``proj`` [tokens, >= 2 heads dim + heads v_dim] holds q, k, v side by side (rows may lie wider apart); ``gates``
+    float32 [tokens, 2 heads] holds the input and forget gates' projections and is overwritten with the gates'
+    logarithms ``cap tanh((g + b) / cap)`` and ``logsigmoid`` of the same; ``state`` [slots, >= mlstm_state_floats]
+    float32. Returns float32 [tokens, heads * v_dim]: S^T q / (max(|n . q|, exp(-m)) + 1e-6)."""
+    _need_cuda(gates, bias_i, bias_f, slots)
+    _check_rows(proj, proj.shape, proj.dtype, "mlstm: proj")
+    n = proj.shape[0]
+    if gates.dtype != torch.float32 or tuple(gates.shape) != (n, 2 * heads):
+        raise KernelError("mlstm: the gates are float32 [tokens, 2 * heads]")
+    if state.dtype != torch.float32 or state.shape[1] < mlstm_state_floats(heads, dim, v_dim) or state.stride(1) != 1:
+        raise KernelError("mlstm: the state is float32 [slots, >= mlstm_state_floats(heads, dim, v_dim)]")
+    _check(lib().ptb_mlstm_gates(_ptr(gates), _ptr(bias_i), _ptr(bias_f), n, heads, ctypes.c_float(cap), _stream(gates)),
+           "mlstm_gates")
+    out = torch.empty((n, heads * v_dim), dtype=torch.float32, device=proj.device)
+    _check(lib().ptb_mlstm_scan(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(gates), _ptr(state), state.stride(0),
+                                _ptr(slots), ctypes.byref(batch), _ptr(out), heads, dim, v_dim, ctypes.c_float(q_scale),
+                                _stream(proj)), "mlstm_scan")
+    return out
+
+
+def head_norm_gate(x: torch.Tensor, gain: torch.Tensor, gate: Optional[torch.Tensor], heads: int, eps: float,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """Every head's stretch of the float32 rows ``x`` [tokens, heads * v_dim] divided by its root mean square, times
+    ``gain`` [heads * v_dim] times sigmoid(``gate``) (of ``out_dtype``; rows may lie wider apart), in ``out_dtype``."""
+    _need_cuda(x, gain)
+    n, width = x.shape
+    if x.dtype != torch.float32 or width % heads or gain.dtype != torch.float32 or gain.numel() != width:
+        raise KernelError("head_norm_gate takes float32 rows [tokens, heads * v_dim] and a float32 gain of that width")
+    out = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    if gate is not None:
+        _check_rows(gate, (n, width), out_dtype, "head_norm_gate: gate")
+    _check(lib().ptb_head_norm_gate(_ptr(x), _ptr(gain), _dtype_code(out), _ptr(gate), 0 if gate is None else gate.stride(0),
+                                    _ptr(out), out.stride(0), n, heads, width // heads, ctypes.c_float(eps), _stream(x)),
+           "head_norm_gate")
     return out

@@ -6,6 +6,8 @@ from .falcon import FALCON_NAME_RULES, falcon_spec
 from .pafevik import pafevik_spec
 from ..config.zalunex import ZalunexConfig
 from .zalunex import zalunex_spec
+from ..config.pogezen import PogezenConfig
+from .pogezen import pogezen_spec
 
 register_architecture(
     "falcon", ("FalconForCausalLM", "RWForCausalLM"), FalconConfig, falcon_spec, name_rules=FALCON_NAME_RULES,
@@ -13,3 +15,4 @@ register_architecture(
 
 register_architecture("pafevik", ("Pafevik",), PafevikConfig, pafevik_spec)
 register_architecture("zalunex", ("Zalunex",), ZalunexConfig, zalunex_spec)
+register_architecture("pogezen", ("Pogezen",), PogezenConfig, pogezen_spec)

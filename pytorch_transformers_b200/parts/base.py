@@ -14,7 +14,9 @@ engine.batch.StepContext of the running step; ``x`` is [tokens, hidden] in the m
 * ``position``:      ``rotation() -> (inv_freq float32 [pairs], pairs) | None`` and
                      ``score_bias() -> slopes float32 [heads] | None``.
 * ``mixer``:         ``forward(x, ctx, entry) -> y``; ``cache_need() -> CacheNeed | None``;
-                     ``state_need() -> StateNeed | None``. ``entry`` is the ScheduleEntry being
+                     ``state_need() -> StateNeed | None``. A mixer with ``fuses_norm(norm) -> bool`` and
+                     ``forward_stream(stream, norm, ctx, entry[, add])`` may take the un-normed stream and form
+                     the block's opening norm in its own first kernel. ``entry`` is the ScheduleEntry being
                      run: it names the cache entry to read and whether to write it. Optional:
                      ``planner()`` (per-step arrays of its own) and ``runs_beside(ctx)``.
 * ``feed_forward``:  ``forward(x, ctx) -> y``.
@@ -90,10 +92,13 @@ class ScheduleEntry:
     """One run of a block. ``block`` indexes ModelSpec.blocks (a block may be named twice);
     ``cache_entry`` names the cache entry its mixer uses (entries are numbered over the whole
     schedule); with ``writes_cache=False`` the mixer only reads an entry that an earlier
-    schedule entry wrote (one layer reading another layer's keys and values)."""
+    schedule entry wrote (one layer reading another layer's keys and values). ``state_offset``: where in the
+    entry's per-sequence state the running mixer's own values begin (a mixer wrapped around another keeps its
+    own values first and hands the inner mixer an entry with a larger offset); ``StepContext.state_of`` reads it."""
     block: int
     cache_entry: int
     writes_cache: bool = True
+    state_offset: int = 0
 
 
 @dataclasses.dataclass
@@ -130,12 +135,14 @@ class CacheNeed:
     """What a mixer wants of the cache for one cache entry. ``kind`` is ``"full"`` (all keys
     and values of the sequence) or ``"window"`` (the last ``window`` of them). ``v_head_dim``: size of a
     value row if it differs from a key row's; 0 for an entry that keeps one row per token only (a mixer
-    whose values are part of its keys: latent attention)."""
+    whose values are part of its keys: latent attention). ``keep_first``: a ``window`` entry whose sequences' first
+    ``keep_first`` positions stay readable for good (their pages are never given back)."""
     kind: str
     kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclasses.dataclass(frozen=True)

@@ -99,7 +99,12 @@ class SequentialBlock(Part):
     def forward(self, x, ctx, entry):
         k = self.build.kernels
         x = resolve(k, x)
-        r = _plus(k, self.mixer, x, self.norm_mixer.forward(x), ctx, entry)
+        fuses = getattr(self.mixer, "fuses_norm", None)
+        if fuses is not None and fuses(self.norm_mixer):
+            # the mixer forms the opening norm in its own first kernel (an elementwise norm under a short convolution)
+            r = self.mixer.forward_stream(x, self.norm_mixer, ctx, entry, add=x)
+        else:
+            r = _plus(k, self.mixer, x, self.norm_mixer.forward(x), ctx, entry)
         if self.feed_forward is None:
             return r
         return _plus(k, self.feed_forward, r, self.norm_ff.forward(r), ctx)

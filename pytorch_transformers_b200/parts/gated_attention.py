@@ -7,7 +7,17 @@
 * a sink: one learned logit per head that takes part in the softmax's normalisation only: ``exp(sink)`` is one
   more term of the denominator, used as stored (``scale`` does not touch it), and nothing is read for it;
 * an output gate: head h's result times sigmoid(W_g x)_h, one number per head, read from the mixer's input;
-* values of a size of their own (``vdim``).
+* values of a size of their own (``vdim``);
+* biases on the four projections (``bias``), added in float32 where queries, keys and values are laid out;
+* a rotation of queries and keys from a ``position`` child, applied before the norm of queries and keys, and a
+  norm without gains (``qk_gain=False``: plain division by the root mean square);
+* first positions that stay visible left of the window (``keep_first``): i sees j if j <= i and
+  (i - j < window or j < keep_first); they keep their true positions;
+* a mixing of the heads' softmax weights after the softmax (``talk``): w'_h(i, j) = sum_g T[h, g] w_g(i, j) with a
+  learned T [heads, heads]; head h applies the mixed weights to the values of its own K/V head. The kernel forms
+  every head's weights on every K/V head's values and a second one sums them with T, which is the same;
+* a mixing of values across layers (``value_mix``): a ``"source"`` layer leaves its values for the later layers of
+  the step; a ``"mix"`` layer caches (1 - lam) v + lam v_source with one learned scalar lam, the same token's values.
 
 score = (q . k) * scale. Query head h reads K/V head h // (heads / kv_heads). Scores, softmax and the
 norms' statistics are float32. The four input projections are one matrix [q | k | v | g] and one product;
@@ -30,7 +40,8 @@ class SinkAttention(Part):
 
     def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int,
                  scale: float, window: int = 0, eps: float = 1e-6, qk_norm: bool = True, sink: bool = True,
-                 gate: bool = True):
+                 gate: bool = True, bias: bool = False, qk_gain: bool = True, keep_first: int = 0, talk: bool = False,
+                 value_mix: str = "none", value_mix_key: str = "values"):
         super().__init__(build, spec)
         if heads % kv_heads:
             raise ValueError(f"heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
@@ -39,19 +50,41 @@ class SinkAttention(Part):
         self.hidden, self.heads, self.kv_heads, self.dim, self.vdim = int(hidden), int(heads), int(kv_heads), int(dim), int(vdim)
         self.scale, self.window, self.eps = float(scale), int(window), float(eps)
         self.qk_norm, self.has_sink, self.has_gate = bool(qk_norm), bool(sink), bool(gate)
+        self.has_bias, self.qk_gain, self.keep_first, self.talk = bool(bias), bool(qk_gain), int(keep_first), bool(talk)
+        if value_mix not in ("none", "source", "mix"):
+            raise ValueError(f"value_mix is 'none', 'source' or 'mix', got {value_mix!r}")
+        if self.keep_first < 0 or (self.keep_first > 0 and self.window <= 0):
+            raise ValueError("keep_first needs a window and must not be negative")
+        if self.talk and (self.has_sink or self.has_gate):
+            raise ValueError("mixed softmax weights go with neither a sink nor an output gate")
+        self.value_mix, self.value_mix_key = value_mix, str(value_mix_key)
+        self.position = self.children.get("position")
+        # the second path: rotation, biases, kept first positions, mixed weights or mixed values
+        self.extended = bool(self.position is not None or self.has_bias or self.keep_first or self.talk
+                             or self.value_mix != "none" or (self.qk_norm and not self.qk_gain))
         self.p_in = self.p_o = self.p_q_norm = self.p_k_norm = self.p_sink = None
+        self.p_in_b = self.p_o_b = self.p_talk = self.p_vmix = None
 
     def param_decls(self) -> Dict[str, ParamDecl]:
         H, G, d, vd = self.heads, self.kv_heads, self.dim, self.vdim
         decls = {"q": ParamDecl((H * d, self.hidden)), "k": ParamDecl((G * d, self.hidden)),
                  "v": ParamDecl((G * vd, self.hidden)), "o": ParamDecl((self.hidden, H * vd))}
-        if self.qk_norm:
+        if self.qk_norm and self.qk_gain:
             decls["q_norm"] = ParamDecl((d,), role="vector", init="one_plus_normal", std=0.1)
             decls["k_norm"] = ParamDecl((d,), role="vector", init="one_plus_normal", std=0.1)
         if self.has_sink:
             decls["sink"] = ParamDecl((H,), role="vector", std=1.0)
         if self.has_gate:
             decls["g"] = ParamDecl((H, self.hidden))
+        if self.has_bias:
+            decls.update({"q_b": ParamDecl((H * d,), role="vector", std=0.5), "k_b": ParamDecl((G * d,), role="vector", std=0.5),
+                          "v_b": ParamDecl((G * vd,), role="vector", std=0.5), "o_b": ParamDecl((self.hidden,), role="vector")})
+            if self.has_gate:
+                decls["g_b"] = ParamDecl((H,), role="vector")
+        if self.talk:
+            decls["talk"] = ParamDecl((H, H), role="vector", std=0.5)
+        if self.value_mix != "none":
+            decls["vmix"] = ParamDecl((), role="vector", std=0.5)     # a source layer stores one too and does not use it
         return decls
 
     def bind(self, t: Dict[str, torch.Tensor]) -> None:
@@ -59,6 +92,10 @@ class SinkAttention(Part):
         self.p_in = torch.cat(rows).contiguous()
         self.p_o = t["o"]
         self.p_q_norm, self.p_k_norm, self.p_sink = t.get("q_norm"), t.get("k_norm"), t.get("sink")
+        if self.has_bias:
+            self.p_in_b = torch.cat([t["q_b"], t["k_b"], t["v_b"]] + ([t["g_b"]] if self.has_gate else [])).contiguous()
+            self.p_o_b = t["o_b"]
+        self.p_talk, self.p_vmix = t.get("talk"), t.get("vmix")
 
     # ---- the projected protocol (parts/pair.py)
     def in_rows(self) -> int:
@@ -77,7 +114,8 @@ class SinkAttention(Part):
         self.p_in = self.p_o = None
 
     def cache_need(self):
-        return CacheNeed("window" if self.window > 0 else "full", self.kv_heads, self.dim, self.window, v_head_dim=self.vdim)
+        return CacheNeed("window" if self.window > 0 else "full", self.kv_heads, self.dim, self.window, v_head_dim=self.vdim,
+                         keep_first=self.keep_first)
 
     def state_need(self):
         return None
@@ -90,6 +128,8 @@ class SinkAttention(Part):
         k = self.build.kernels
         k_pool, v_pool, group = ctx.cache.entry_storage(entry.cache_entry)
         batch = ctx.batch_c[group]
+        if self.extended:
+            return self._forward_extended(proj, ctx, entry, out, out_scale, k_pool, v_pool, batch)
         q = k.qk_norm_store(proj, k_pool, v_pool, batch, self.p_q_norm, self.p_k_norm, self.heads, self.kv_heads, self.dim,
                             self.vdim, self.eps, write_cache=entry.writes_cache)
         gate = proj[:, self.in_rows() - self.heads:] if self.has_gate else None
@@ -114,6 +154,35 @@ class SinkAttention(Part):
                             None, self.kv_heads, self.scale, self.window, sinks=self.p_sink, gate=gate, out_scale=out_scale,
                             out=out)
 
+    def _forward_extended(self, proj, ctx, entry, out, out_scale, k_pool, v_pool, batch) -> None:
+        k = self.build.kernels
+        if self.qk_norm and self.qk_gain:
+            raise ValueError("sink_attention: a rotation, biases, kept first positions, mixed weights or mixed values go "
+                             "with a norm of queries and keys without gains (qk_gain=False) or none")
+        if self.has_gate and self.has_bias:
+            raise ValueError("sink_attention: an output gate with a bias is not built")
+        H, G, d, vd = self.heads, self.kv_heads, self.dim, self.vdim
+        first = ctx.shared.get(self.value_mix_key) if self.value_mix == "mix" else None
+        if self.value_mix == "mix" and first is None:
+            raise ValueError(f"sink_attention: no earlier layer of this step left values under {self.value_mix_key!r}")
+        res = k.rope_norm_store(proj, self.p_in_b, k_pool, v_pool, batch, ctx.rope(self.position), H, G, d, vd, self.eps,
+                                unit_norm=self.qk_norm, v_first=first, lam=self.p_vmix, keep_values=self.value_mix == "source",
+                                write_cache=entry.writes_cache)
+        if self.value_mix == "source":
+            q, ctx.shared[self.value_mix_key] = res
+        else:
+            q = res
+        tiles = ctx.plan(AttentionTiles.plan_key)
+        args = (q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"], tiles.facts["n_tiles"], None, G,
+                self.scale, self.window)
+        if self.talk:
+            if out_scale != 1.0:
+                raise ValueError("sink_attention: mixed softmax weights take no output factor")
+            k.talk_mix(k.attention_generic(*args, keep_first=self.keep_first, wide=True), self.p_talk, q.dtype, out=out)
+            return
+        gate = proj[:, self.in_rows() - H:] if self.has_gate else None
+        k.attention_generic(*args, sinks=self.p_sink, gate=gate, out_scale=out_scale, out=out, keep_first=self.keep_first)
+
     def _decode_splits(self, ctx, hpk: int) -> int:
         """Blocks per (sequence, K/V head) in a step of single tokens: enough to fill the device, each with two
         pages of visible keys at least."""
@@ -125,9 +194,11 @@ class SinkAttention(Part):
             pages = min(pages, self.window // k.PAGE + 2)
         return max(1, min((2 * k.sm_count(self.build.device)) // blocks, pages // 2, 64))
 
-    def forward(self, x, ctx, entry):
+    fuses_add = True
+
+    def forward(self, x, ctx, entry, add=None):
         k = self.build.kernels
-        proj = linear(k, x, self.p_in)
+        proj = linear(k, x, self.p_in)      # biases, where there are any, are added where q, k, v are laid out
         heads = torch.empty((x.shape[0], self.out_columns()), dtype=x.dtype, device=x.device)
         self.forward_projected(proj, ctx, entry, heads)
-        return linear(k, heads, self.p_o)
+        return linear(k, heads, self.p_o, self.p_o_b, add=add)

@@ -48,6 +48,10 @@ def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
                 y = kernels.skinny_linear(x, weight, out_dtype=torch.float32)
             else:
                 y = kernels.matmul_nt(x, weight, out_dtype=torch.float32)
+        elif act == "none":
+            # with a bias: the float32 sums take the bias before they meet the stream, still unrounded
+            y = linear(kernels, x, weight, wide_out=True)
+            kernels.bias_act_(y, bias, "none")
         else:
             y = linear(kernels, x, weight, bias, act)
         return kernels.add_stream(add, y)

@@ -81,7 +81,7 @@ class LinearAttention(Part):
 
     def forward_projected(self, proj, ctx, entry, out, out_scale: float = 1.0) -> None:
         k = self.build.kernels
-        state = ctx.cache.entry_state(entry.cache_entry)
+        state = ctx.state_of(entry, self.state_need().numel)
         plan = ctx.plan(RecurrenceChunks.plan_key)
         chunks = None
         if plan.facts["n_chunks"] and k.linear_attention_chunks_supports(self.dim, self.vdim):

@@ -1,4 +1,5 @@
-"""Norm parts: LayerNorm and RMSNorm over the hidden axis, statistics in float32.
+"""Norm parts: LayerNorm and RMSNorm over the hidden axis, statistics in float32, and the Dynamic Tanh norm
+(``dyt``: ``tanh(alpha x) * weight + bias`` with one learned scalar ``alpha``; elementwise, no statistics at all).
 
 ``torch.nn.LayerNorm(hidden, eps)`` is every norm of the reference's Falcon
 (src/transformers/models/falcon/modeling_falcon.py:603-612, 843): biased variance, gain and bias.
@@ -80,3 +81,31 @@ class RMSNorm(LayerNorm):
         super().bind(tensors)
         if self.one_plus:
             self.p_weight = self.p_weight + 1.0
+
+
+@register_part("norm", "dyt")
+class DynamicTanh(Part):
+    """y = tanh(alpha * x) * weight + bias, in float32; ``alpha`` is a scalar parameter. Nothing is reduced over the
+    row, so a kernel that reads the rows anyway can form it on the way (``parts/input_conv.py`` does)."""
+    kind = "dyt"
+    graph_safe = True
+
+    def __init__(self, build: BuildContext, spec: PartSpec, size: int, bias: bool = True):
+        super().__init__(build, spec)
+        self.size, self.has_bias = int(size), bool(bias)
+        self.p_weight = self.p_bias = self.p_alpha = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        d = {"weight": ParamDecl((self.size,), role="vector", init="one_plus_normal", std=0.1),
+             "alpha": ParamDecl((), role="vector", init="one_plus_normal", std=0.1)}
+        if self.has_bias:
+            d["bias"] = ParamDecl((self.size,), role="vector", init="normal", std=0.1)
+        return d
+
+    def out_dtype(self, x):
+        """A float32 stream of a bfloat16 model is normed into bfloat16; anything else keeps its type."""
+        import torch
+        return self.build.dtype if x.dtype == torch.float32 else x.dtype
+
+    def forward(self, x):
+        return self.build.kernels.dyt(x, self.p_alpha, self.p_weight, self.p_bias, self.out_dtype(x))

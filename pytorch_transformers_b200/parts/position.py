@@ -33,7 +33,7 @@ class NoPosition(Part):
 @register_part("position", "rotary")
 class RotaryPosition(NoPosition):
     def __init__(self, build: BuildContext, spec: PartSpec, head_dim: int, theta: float, factor: float = 1.0,
-                 rotary_dim: int = 0, interleaved: bool = False):
+                 rotary_dim: int = 0, interleaved: bool = False, yarn: dict = None):
         super().__init__(build, spec)
         # which dims make a rotated pair: (i, i + dim / 2), the reference's rotate_half, or (2 i, 2 i + 1)
         self.interleaved = bool(interleaved)
@@ -44,12 +44,34 @@ class RotaryPosition(NoPosition):
         inv_freq = 1.0 / (float(theta) ** exponent)
         if factor != 1.0:
             inv_freq = inv_freq / float(factor)
+        self.table_scale = 1.0
+        if yarn:
+            inv_freq, self.table_scale = yarn_frequencies(dim, float(theta), **yarn)
         self.inv_freq = inv_freq.to(torch.float32).to(build.device)
         # layers whose rotation has the same constants share one table of angles per step
-        self.rotation_key = ("rotary", dim, float(theta), float(factor))
+        self.rotation_key = ("rotary", dim, float(theta), float(factor), tuple(sorted((yarn or {}).items())))
 
     def rotation(self):
         return self.inv_freq
+
+
+def yarn_frequencies(dims: int, base: float, factor: float, original: float, fast: float, slow: float):
+    """YaRN: frequencies that turn often within the ``original`` context stay as they are, those that turn seldom are
+    divided by ``factor``, with a linear ramp between. With d(t) = dims ln(original / (2 pi t)) / (2 ln base) the
+    index at which a frequency makes t turns over the original context, the ramp runs from lo = max(floor(d(fast)), 0)
+    to hi = min(ceil(d(slow)), dims - 1): r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) and
+    f_i' = (f_i / factor) r_i + f_i (1 - r_i). Cosines and sines are multiplied by 0.1 ln(factor) + 1. Computed in
+    float64; returns (frequencies [dims / 2], that multiplier)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+
+    def index_of(turns: float) -> float:
+        return dims * math.log(float(original) / (2.0 * math.pi * float(turns))) / (2.0 * math.log(float(base)))
+
+    lo = max(math.floor(index_of(fast)), 0)
+    hi = min(math.ceil(index_of(slow)), dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / float(factor) * ramp + f * (1.0 - ramp), 0.1 * math.log(float(factor)) + 1.0
 
 
 def alibi_slopes(heads: int) -> torch.Tensor:

@@ -93,7 +93,7 @@ class GatedLinearRecurrence(Part):
         k = self.build.kernels
         t, R, B = x.shape[0], self.width, self.blocks
         proj = linear(k, x, self.p_yx)
-        state = ctx.cache.entry_state(entry.cache_entry)
+        state = ctx.state_of(entry, self.state_need().numel)
         slots, batch = ctx.dev["slots"], ctx.batch_c[0]
         y_act, u = k.rglru_conv(proj, self.p_y_b, self.p_x_b, self.p_conv, self.p_conv_b, state, slots, batch)
         gates = k.block_linear(u.view(t, B, R // B), self.p_gates, self.p_gates_b, act="sigmoid", out_dtype=torch.float32)
