@@ -72,7 +72,8 @@ def main(argv=None) -> int:
     from ..modeling import AutoModelForCausalLM
     from .. import native
     native.library()
-    model = AutoModelForCausalLM.from_pretrained(args.model, dtype=args.dtype, device="cuda")
+    # tensors that the model does not ask for are reported and left alone
+    model = AutoModelForCausalLM.from_pretrained(args.model, dtype=args.dtype, device="cuda", strict=False)
     # the count is of tokens; every live request rounds its own up to a whole page, so there is room for
     # that remainder of many requests
     cache = model.new_cache(max(args.max_tokens, 64) + 64 * PAGE)

@@ -86,7 +86,9 @@ def load_weights(model, folder: str, name_rules: Optional[dict] = None, strict: 
                 continue
             f, real = stored[name]
             e = f.entries[real]
-            if tuple(e.shape) != tuple(decl.shape):
+            if tuple(decl.shape) == () and tuple(e.shape) == (1,):
+                pass        # a scalar stored as one element
+            elif tuple(e.shape) != tuple(decl.shape):
                 mismatched.append(f"{name}: stored {list(e.shape)}, model wants {list(decl.shape)}")
             elif decl.role == "int" and e.dtype.is_floating_point:
                 mismatched.append(f"{name}: stored as {e.dtype}, model wants an integer table")
@@ -102,7 +104,7 @@ def load_weights(model, folder: str, name_rules: Optional[dict] = None, strict: 
         for name, (part, logical, decl) in table.items():
             f, real = stored[name]
             host = f.tensor(real)
-            tensors[name] = host.to(device=model.device, dtype=model.device_dtype(decl))
+            tensors[name] = host.reshape(tuple(decl.shape)).to(device=model.device, dtype=model.device_dtype(decl))
         if tied_head and "lm_head.weight" in stored:
             f, real = stored["lm_head.weight"]
             head = f.tensor(real)

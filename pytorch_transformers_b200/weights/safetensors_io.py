@@ -186,6 +186,6 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], me
                                        f"({name!r} {dtype} {tuple(shape)})")
             t = t.detach().cpu().contiguous()
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dtype == torch.bfloat16
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype == torch.bfloat16
                         else t.numpy().tobytes())
     os.replace(tmp, path)

@@ -132,7 +132,7 @@ def write_safetensors(path: str, tensors: Dict[str, np.ndarray], metadata=None) 
     if metadata is not None:
         header["__metadata__"] = metadata
     for name, arr in tensors.items():
-        arr = np.ascontiguousarray(arr)
+        arr = np.ascontiguousarray(arr).reshape(np.shape(arr))     # a scalar stays a scalar
         b = arr.tobytes()
         header[name] = {"dtype": codes[arr.dtype], "shape": list(arr.shape), "data_offsets": [off, off + len(b)]}
         blobs.append(b)
