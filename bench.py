@@ -571,7 +571,8 @@ class KernelTimes:
              "attention_generic", "attention_decode", "attention_decode_tc", "latent_store", "latent_attention",
              "latent_unfolded_attention",
              "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_",
-             "embed_sum", "post_norm_add", "qk_norm_store", "linear_attention", "norm_gate", "glu_clamp", "softcap_")
+             "embed_sum", "post_norm_add", "qk_norm_store", "linear_attention", "norm_gate", "glu_clamp", "softcap_",
+             "dyt", "mlstm", "head_norm_gate", "rope_norm_store", "talk_mix")
 
     def __init__(self, kernels):
         self.k, self.records, self.saved = kernels, [], {}
@@ -840,9 +841,116 @@ def run_zalunex(args):
     return 0
 
 
+# ---- Pogezen beside Zalunex at equal size (`--only pogezen [--size s|m]`) ----
+# Sizes that resemble a served model's layers: the width; four layers that take turns between a matrix memory of 16
+# or 32 heads of 128 x 128 with capped exponential gates and an attention of as many heads of 128 on a quarter as many
+# K/V heads, rotated on half of each head with a stretched rotation, a window of 1,024 that keeps the first 4 tokens,
+# mixed softmax weights and mixed values; an input convolution of 4 taps; squared-relu feed-forwards 4 x the width
+# wide. Zalunex beside it is `--only zalunex`'s model of the same width, heads and layers: the library's other design
+# with a float32 stream, a windowed attention and a matrix state per head.
+def pogezen_config(size):
+    z = PAFEVIK_SIZES[size]
+    w, heads = z["width"], z["heads"]
+    mem = {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    att = {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "mask": {"size": 1024, "keep_first": 4},
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+           "v_mix": True}
+    mlp = {"kind": "dense", "ff": 4 * w}
+    return {"architecture": "Pogezen", "vocab": 32000, "width": w, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "canon": {"taps": 4},
+            "layers": [{"type": t, "mixer": dict(m), "mlp": mlp} for t, m in (("mlstm", mem), ("attention", att)) * 2]}
+
+
+def run_pogezen(args):
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+    tokens, batch, context = args.prefill_tokens, args.batch, args.context
+    raw = pogezen_config(args.size)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    mem, att, w = raw["layers"][0]["mixer"], raw["layers"][1]["mixer"], raw["width"]
+    result = {"only": "pogezen", "size": args.size, "prefill_tokens": tokens, "batch": batch, "context": context,
+              "config": {"width": w, "layers": len(raw["layers"]), "heads": att["heads"]}}
+    for name, make in (("pogezen", lambda: ptb.AutoModelForCausalLM.from_config(ptb.PogezenConfig.from_dict(raw), seed=0, dtype="bfloat16")),
+                       ("zalunex", lambda: ptb.AutoModelForCausalLM.from_config(ptb.ZalunexConfig.from_dict(zalunex_config(args.size)),
+                                                                               seed=0, dtype="bfloat16"))):
+        model = make()
+        result[name] = measure_prefill_and_decode(model, args, gen, flush)
+        del model
+        torch.cuda.empty_cache()
+    G, Z = result["pogezen"], result["zalunex"]
+
+    def per_call(table, key):
+        return table[key]["ms"] / table[key]["calls"] if key in table else None
+
+    roof = {}
+    H, K, d, vd = att["heads"], att["kv_heads"], att["dim"], att["vdim"]
+    keep, size = att["mask"]["keep_first"], att["mask"]["size"]
+    seen = sum(min(t + 1, size) + max(0, min(keep, t + 1 - size)) for t in range(tokens))     # visible (query, key) pairs
+    # the attention with mixed weights: scores of every head, then every head's weights on every K/V head's values
+    for key in ("attention_generic", "attention_mma"):
+        t = per_call(G["prefill_kernels_ms"], key)
+        if t:
+            roof[f"talk_{key}_prefill_TFLOPs_as_run"] = round(H * seen * 2 * (d + K * vd) / t / 1e9, 1)
+            roof[f"talk_{key}_prefill_TFLOPs_needed"] = round(H * seen * 2 * (d + vd) / t / 1e9, 1)
+            roof[f"talk_{key}_prefill_frac_of_burst"] = round(roof[f"talk_{key}_prefill_TFLOPs_as_run"] / pk["bf16_tflops"], 4)
+        t = per_call(Z["prefill_kernels_ms"], key)
+        if t:
+            zl = zalunex_config(args.size)["layers"][0]["mixer"]["left"]
+            zseen = sum(min(t_ + 1, zl["mask"]["size"]) for t_ in range(tokens))
+            roof[f"zalunex_{key}_prefill_TFLOPs"] = round(zl["heads"] * zseen * 2 * (zl["dim"] + zl["vdim"]) / t / 1e9, 1)
+            roof[f"zalunex_{key}_prefill_frac_of_burst"] = round(roof[f"zalunex_{key}_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    mh, md, mv = mem["heads"], mem["dim"], mem["vdim"]
+    t = per_call(G["prefill_kernels_ms"], "mlstm")
+    if t:   # per chunk of 64: scores, scores x values, queries x state, keys x values; q, k, v, gates in, float32 rows out
+        flops = mh * tokens * 2 * (64 * md / 2 + 64 * mv / 2 + 2 * md * mv)
+        io = tokens * mh * (2 * (2 * md + mv) + 8 + 4 * mv)
+        roof["mlstm_prefill_TFLOPs"] = round(flops / t / 1e9, 1)
+        roof["mlstm_prefill_GBps"] = round(io / t / 1e6, 1)
+        roof["mlstm_prefill_frac_of_hbm"] = round(roof["mlstm_prefill_GBps"] / pk["hbm_gbs"], 4)
+    t = per_call(Z["prefill_kernels_ms"], "linear_attention")
+    if t:
+        r = zalunex_config(args.size)["layers"][0]["mixer"]["right"]
+        io = tokens * r["heads"] * (2 * (2 * r["dim"] + r["vdim"]) + 4 * r["vdim"])
+        roof["zalunex_linear_attention_prefill_GBps"] = round(io / t / 1e6, 1)
+        roof["zalunex_linear_attention_prefill_frac_of_hbm"] = round(roof["zalunex_linear_attention_prefill_GBps"] / pk["hbm_gbs"], 4)
+    t = G["prefill_kernels_ms"].get("matmul_nt")
+    if t:   # all library products of the prompt
+        n_mem = 2 * mh * md + 2 * mh * mv + 2 * mh + mh * mv
+        n_att = (H + K) * d + K * vd + H * vd
+        flops = 2 * tokens * w * (2 * n_mem + 2 * n_att + 4 * 2 * 4 * w)
+        roof["library_products_TFLOPs"] = round(flops / t["ms"] / 1e9, 1)
+        roof["library_products_frac_of_burst"] = round(roof["library_products_TFLOPs"] / pk["bf16_tflops"], 4)
+    for key, bytes_per_row in (("dyt", w * (4 + 2)), ("head_norm_gate", mh * mv * (4 + 2 + 2)),
+                               ("rope_norm_store", ((H + K) * d + K * vd) * 4), ("talk_mix", H * vd * (4 * K + 2)),
+                               ("mlstm_gates", 0)):
+        t = per_call(G["prefill_kernels_ms"], key)
+        if t and bytes_per_row:
+            roof[f"{key}_prefill_GBps"] = round(tokens * bytes_per_row / t / 1e6, 1)
+            roof[f"{key}_prefill_frac_of_hbm"] = round(roof[f"{key}_prefill_GBps"] / pk["hbm_gbs"], 4)
+    zw = zalunex_config(args.size)["width"]
+    for key, bytes_per_row in (("post_norm_add", zw * (4 + 4 + 4 + 2)), ("norm_gate", H * 128 * (4 + 2 + 2)),
+                               ("qk_norm_store", (H + 2 * K) * 128 * 4)):
+        t = per_call(Z["prefill_kernels_ms"], key)
+        if t:
+            roof[f"zalunex_{key}_prefill_GBps"] = round(tokens * bytes_per_row / t / 1e6, 1)
+            roof[f"zalunex_{key}_prefill_frac_of_hbm"] = round(roof[f"zalunex_{key}_prefill_GBps"] / pk["hbm_gbs"], 4)
+    result["roofline"] = roof
+    result["peaks"] = pk
+    print(json.dumps(result))
+    return 0
+
+
 def run_ours(args):
     if args.only == "pafevik":
         return run_pafevik(args)
+    if args.only == "pogezen":
+        return run_pogezen(args)
     if args.only == "zalunex":
         return run_zalunex(args)
     if args.only == "sample":
@@ -1120,10 +1228,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "prefill-attention", "config", "linear",
-                             "fill", "mma-cadence", "pafevik", "zalunex"],
+                             "fill", "mma-cadence", "pafevik", "zalunex", "pogezen"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
-    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik and --only zalunex")
+    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik, --only zalunex and --only pogezen")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
     ap.add_argument("--past", type=int, default=0, help="cached tokens before the prompt for --only prefill-attention")

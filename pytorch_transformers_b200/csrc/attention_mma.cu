@@ -28,6 +28,11 @@ struct MmaParams {
   // the softmax weights meet the values as two bfloat16 terms, the rounded weight and the rounded rest (16 bits of
   // mantissa together), in two instructions: for designs that want their attention weights in 32-bit
   int wide_weights;
+  // with a window, a sequence's first keep_first positions stay visible left of it; their pages are walked first
+  int keep_first;
+  // not null: every head's weights on every K/V head's values, float32 [tokens][heads][kv_heads][D]; blockIdx.y then
+  // also walks the K/V head whose values a block reads, and `out`, sinks, gate and factor are not used
+  float* out_wide;
 };
 
 // What a row's accumulated O is multiplied by at the end: 1 / (sum of the keys' weights + the sink's weight), the
@@ -63,8 +68,10 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   const int tile = blockIdx.x;
   const int qpk = p.heads / p.kv_heads;
   const int chunks = (qpk + p.hpk - 1) / p.hpk;
-  const int g = blockIdx.y / chunks;           // K/V head
-  const int h0 = (blockIdx.y % chunks) * p.hpk;  // first head of the chunk within the group
+  const int by = p.out_wide ? blockIdx.y / p.kv_heads : blockIdx.y;
+  const int g = by / chunks;           // K/V head of the keys
+  const int gv = p.out_wide ? blockIdx.y % p.kv_heads : g;   // K/V head of the values
+  const int h0 = (by % chunks) * p.hpk;  // first head of the chunk within the group
   const int split = blockIdx.z;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
@@ -115,11 +122,14 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   int kb_first = 0;
   if (p.window > 0) kb_first = max(0, past + q0 - p.window + 1) / KEYS;
   const int kb_end_all = last_pos / KEYS + 1;
-  const int n_pages = kb_end_all - kb_first;
+  // pages of the kept first positions that lie left of the window's first page come first in the walk
+  const int n_keep = (p.window > 0 && p.keep_first > 0) ? min((p.keep_first + KEYS - 1) / KEYS, kb_first) : 0;
+  const int n_pages = kb_end_all - kb_first + n_keep;
   const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
-  const int kb_begin = kb_first + split * per_split;
-  const int kb_end = min(kb_end_all, kb_begin + per_split);
+  const int kb_begin = split * per_split;                   // places in the walk, not page numbers
+  const int kb_end = min(n_pages, kb_begin + per_split);
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
+  auto page_at = [&](int i) { return i < n_keep ? i : kb_first + (i - n_keep); };
 
   float o[D / 8][4];
 #pragma unroll
@@ -131,18 +141,19 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 
   if (kb_begin < kb_end) {
     {
-      const int page = pages[kb_begin];
+      const int page = pages[page_at(kb_begin)];
       load_page<D>(smem_base, k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
-      load_page<D>(smem_base + TILE_BYTES, v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
+      load_page<D>(smem_base + TILE_BYTES, v_pool + kv_offset(page, gv, 0, p.kv_heads, D), tid, nthreads);
       cp_async_commit();
     }
-    for (int kb = kb_begin; kb < kb_end; ++kb) {
-      const int stage = (kb - kb_begin) & 1;
-      if (kb + 1 < kb_end) {
-        const int page = pages[kb + 1];
+    for (int at = kb_begin; at < kb_end; ++at) {
+      const int kb = page_at(at);
+      const int stage = (at - kb_begin) & 1;
+      if (at + 1 < kb_end) {
+        const int page = pages[page_at(at + 1)];
         const uint32_t dst = smem_base + (stage ^ 1) * 2 * TILE_BYTES;
         load_page<D>(dst, k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
-        load_page<D>(dst + TILE_BYTES, v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
+        load_page<D>(dst + TILE_BYTES, v_pool + kv_offset(page, gv, 0, p.kv_heads, D), tid, nthreads);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
@@ -189,7 +200,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             const int i = e >> 1;
             const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
             bool visible = key_pos <= row_pos[i];
-            if (p.window > 0) visible = visible && key_pos > row_pos[i] - p.window;
+            if (p.window > 0) visible = visible && (key_pos > row_pos[i] - p.window || key_pos < p.keep_first);
             float v = s[j][e];
             if (alibi_slopes) v += alibi_bias(slope[i], key_pos);
             v = visible ? v * sl2 : -INFINITY;
@@ -264,6 +275,14 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     for (int i = 0; i < 2; ++i) {
       if (!row_ok[i]) continue;
       const int token = start + q0 + row_tok[i], head = g * qpk + h0 + row_head[i];
+      if (p.out_wide) {
+        const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+        float* dst = p.out_wide + ((size_t(token) * p.heads + head) * p.kv_heads + gv) * D + t4 * 2;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j)
+          *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+        continue;
+      }
       const float inv = finish_row(p, m_run[i], l_run[i], token, head);
       __nv_bfloat16* dst = out + size_t(token) * p.out_stride + size_t(head) * D + t4 * 2;
 #pragma unroll
@@ -303,7 +322,8 @@ attention_mma_reduce_kernel(const float* __restrict__ part_o, const float* __res
   if (r >= rows_total) return;
   const int qpk = p.heads / p.kv_heads;
   const int chunks = (qpk + p.hpk - 1) / p.hpk;
-  const int g = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * p.hpk;
+  const int by = p.out_wide ? blockIdx.y / p.kv_heads : blockIdx.y;
+  const int g = by / chunks, h0 = (by % chunks) * p.hpk;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int tok = r / p.hpk, hh = r % p.hpk;
   if (tok >= min(p.tokens_per_tile, sb.seq_new[seq] - q0) || hh >= min(p.hpk, qpk - h0)) return;
@@ -328,6 +348,13 @@ attention_mma_reduce_kernel(const float* __restrict__ part_o, const float* __res
     }
   }
   const int token = sb.seq_start[seq] + q0 + tok, head = g * qpk + h0 + hh;
+  if (p.out_wide) {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float* dst = p.out_wide + ((size_t(token) * p.heads + head) * p.kv_heads + blockIdx.y % p.kv_heads) * D + lane * PER;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) dst[e] = acc[e] * inv;
+    return;
+  }
   const float inv = finish_row(p, m, l, token, head);
   __nv_bfloat16* dst = out + size_t(token) * p.out_stride + size_t(head) * D + lane * PER;
 #pragma unroll
@@ -356,14 +383,15 @@ int launch_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
       configured[dev] = true;
     }
   }
-  dim3 grid(n_tiles, p.kv_heads * chunks, p.n_splits);
+  const int y_blocks = p.kv_heads * chunks * (p.out_wide ? p.kv_heads : 1);
+  dim3 grid(n_tiles, y_blocks, p.n_splits);
   const bool partial = p.n_splits > 1;
   attention_mma_kernel<D><<<grid, warps * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out,
       partial ? part_o : nullptr, partial ? part_ml : nullptr, sb, tile_seq, tile_q0, slopes, p);
   if (cudaGetLastError() != cudaSuccess) return PTB_ERR_LAUNCH;
   if (partial) {
-    dim3 rgrid(n_tiles, p.kv_heads * chunks, (warps * 16 + 3) / 4);
+    dim3 rgrid(n_tiles, y_blocks, (warps * 16 + 3) / 4);
     attention_mma_reduce_kernel<D><<<rgrid, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, sb, tile_seq,
                                                              tile_q0, p, warps * 16);
   }
@@ -389,28 +417,35 @@ PTB_API long long ptb_attention_mma_scratch_floats(int n_tiles, int heads, int k
 // sinks [heads] float32, gate (bfloat16, row t head h at gate[t * gate_stride + h]), out_scale and out_stride
 // (elements between two tokens' output rows; 0: heads * head_dim) and wide_weights as MmaParams says; null, null, 0, 1,
 // 0, 0: plain attention.
-PTB_API int ptb_attention_mma_gated(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+// keep_first: with a window, the sequence's first keep_first positions stay visible too. out_wide (float32
+// [tokens, heads, kv_heads, head_dim]; then out, sinks and gate are null and out_scale 1): every head's softmax
+// weights applied to every K/V head's values; the scratch of a launch with splits is kv_heads times as large.
+PTB_API int ptb_attention_mma_kept(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                               const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
                               const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
                               int tokens_per_tile, int n_splits, int warps, float scale, int window,
                               const float* sinks, const void* gate, int gate_stride, float out_scale, int out_stride,
-                              int wide_weights, cudaStream_t stream) {
+                              int wide_weights, int keep_first, float* out_wide, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
   if (out_stride == 0) out_stride = heads * head_dim;
   if (out_stride < heads * head_dim || out_stride % 2 != 0 || (gate != nullptr && gate_stride < heads)) return PTB_ERR_SIZE;
+  if (keep_first < 0 || (out_wide != nullptr && (out != nullptr || sinks != nullptr || gate != nullptr || out_scale != 1.f)))
+    return PTB_ERR_SIZE;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || warps < 1 || warps > 8 || hpk < 1 ||
       tokens_per_tile < 1 || hpk * tokens_per_tile > warps * 16 || n_splits < 1 || n_splits > 65535)
     return PTB_ERR_SIZE;
   const int qpk = heads / kv_heads;
   const int chunks = (qpk + hpk - 1) / hpk;
-  if (kv_heads * chunks > 65535) return PTB_ERR_SIZE;
+  const int y_blocks = kv_heads * chunks * (out_wide ? kv_heads : 1);
+  if (y_blocks > 65535) return PTB_ERR_SIZE;
   if (n_splits > 1 && scratch == nullptr) return PTB_ERR_SIZE;
   MmaParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.tokens_per_tile = tokens_per_tile; p.n_splits = n_splits;
   p.scale = scale; p.window = window;
   p.sinks = sinks; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride; p.out_scale = out_scale;
   p.out_stride = out_stride; p.wide_weights = wide_weights;
-  const long long o_floats = (long long)n_tiles * kv_heads * chunks * n_splits * (warps * 16) * head_dim;
+  p.keep_first = window > 0 ? keep_first : 0; p.out_wide = out_wide;
+  const long long o_floats = (long long)n_tiles * y_blocks * n_splits * (warps * 16) * head_dim;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + o_floats : nullptr;
   switch (head_dim) {
@@ -423,6 +458,17 @@ PTB_API int ptb_attention_mma_gated(const void* q, const void* k_pool, const voi
     default:
       return PTB_ERR_SIZE;
   }
+}
+
+PTB_API int ptb_attention_mma_gated(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+                              const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                              const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
+                              int tokens_per_tile, int n_splits, int warps, float scale, int window,
+                              const float* sinks, const void* gate, int gate_stride, float out_scale, int out_stride,
+                              int wide_weights, cudaStream_t stream) {
+  return ptb_attention_mma_kept(q, k_pool, v_pool, out, scratch, sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
+                                kv_heads, head_dim, hpk, tokens_per_tile, n_splits, warps, scale, window, sinks, gate,
+                                gate_stride, out_scale, out_stride, wide_weights, 0, nullptr, stream);
 }
 
 PTB_API int ptb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,

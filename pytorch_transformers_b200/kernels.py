@@ -84,7 +84,7 @@ def lib():
     if not _configured:
         for name in ("ptb_gather_rows", "ptb_norm", "ptb_bias_act", "ptb_residual", "ptb_to_float",
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
-                     "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports",
+                     "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_kept", "ptb_attention_mma_supports",
                      "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
@@ -100,10 +100,12 @@ def lib():
                      "ptb_attention_mma_gated", "ptb_linear_attention_chunk_join", "ptb_linear_attention_mma_supports",
                      "ptb_linear_attention_chunks_mma", "ptb_linear_attention_token", "ptb_dyt", "ptb_mlstm_gates",
                      "ptb_mlstm_scan", "ptb_mlstm_max_dim", "ptb_mlstm_state_floats", "ptb_head_norm_gate",
-                     "ptb_rope_norm_store", "ptb_talk_mix"):
+                     "ptb_rope_norm_store", "ptb_talk_mix", "ptb_mlstm_chunks", "ptb_mlstm_chunks_supports",
+                     "ptb_mlstm_chunk_tokens"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
+        L.ptb_mlstm_chunks_scratch_floats.restype = ctypes.c_longlong
         _configured = True
     return L
 
@@ -528,39 +530,51 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, b
                   kv_heads: int, scale: float, window: int, tokens_per_tile: int, heads_per_tile: int, warps: int,
                   n_splits: int, scratch: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
                   gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
-                  out: Optional[torch.Tensor] = None, wide_weights: bool = False) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, wide_weights: bool = False, keep_first: int = 0,
+                  wide: bool = False) -> torch.Tensor:
     """Tensor-core attention over the paged cache (bfloat16). A tile holds ``tokens_per_tile`` tokens
     x ``heads_per_tile`` heads of one K/V group in ``warps`` x 16 rows; with ``n_splits`` > 1 the key
     pages are divided among blocks and joined by a second kernel (``scratch``: float32 workspace).
     ``sinks``, ``gate``, ``out_scale``, ``out``: as attention_generic takes them. ``wide_weights``: the softmax
-    weights meet the values as two bfloat16 terms (16 bits of mantissa) instead of one."""
+    weights meet the values as two bfloat16 terms (16 bits of mantissa) instead of one. ``keep_first``: with a window,
+    the first positions that stay visible left of it. ``wide``: every head's weights on every K/V head's values, float32
+    [tokens, heads, kv_heads, head_dim], as ``attention_generic(wide=True)`` returns them."""
     _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, scratch, sinks)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_mma takes bfloat16 tensors")
     n, heads, head_dim = q.shape
-    if out is None:
-        out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
-    _check_rows(out, (n, heads * head_dim), q.dtype, "attention_mma: out")
+    out_wide = None
+    if wide:
+        if sinks is not None or gate is not None or out_scale != 1.0 or out is not None:
+            raise KernelError("attention_mma: the wide form takes no sink, gate, factor or output view")
+        out_wide = torch.empty((n, heads, kv_heads, head_dim), dtype=torch.float32, device=q.device)
+    else:
+        if out is None:
+            out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+        _check_rows(out, (n, heads * head_dim), q.dtype, "attention_mma: out")
+        if out.data_ptr() % 4 or out.stride(0) % 2:
+            raise KernelError("attention_mma: output rows must start at whole 32-bit words")
     if gate is not None:
         _check_rows(gate, (n, heads), q.dtype, "attention_mma: gate")
-    if out.data_ptr() % 4 or out.stride(0) % 2:
-        raise KernelError("attention_mma: output rows must start at whole 32-bit words")
     if n_splits > 1:
         need = attention_mma_scratch_floats(n_tiles, heads, kv_heads, heads_per_tile, n_splits, warps, head_dim)
+        if wide:
+            need *= kv_heads
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         elif scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"attention_mma: scratch of {need} float32 values needed")
-    _check(lib().ptb_attention_mma_gated(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
-                                         ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
-                                         heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
-                                         ctypes.c_float(scale), window, _ptr(sinks), _ptr(gate),
-                                         0 if gate is None else gate.stride(0), ctypes.c_float(out_scale), out.stride(0),
-                                         1 if wide_weights else 0, _stream(q)), "attention_mma")
+    _check(lib().ptb_attention_mma_kept(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
+                                        ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                        heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
+                                        ctypes.c_float(scale), window, _ptr(sinks), _ptr(gate),
+                                        0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
+                                        0 if wide else out.stride(0), 1 if wide_weights else 0, int(keep_first),
+                                        _ptr(out_wide), _stream(q)), "attention_mma")
     if n_splits > 1:
         global launches
         launches += 1   # the kernel that joins the splits
-    return out
+    return out_wide if wide else out
 
 
 def attention_mma_scratch_floats(n_tiles: int, heads: int, kv_heads: int, heads_per_tile: int, n_splits: int,
@@ -1242,14 +1256,26 @@ def mlstm_state_floats(heads: int, dim: int, v_dim: int) -> int:
     return heads * (dim * v_dim + ((v_dim + 31) // 32) * (dim + 1))
 
 
+MLSTM_CHUNK = 64   # ptb_mlstm_chunk_tokens()
+
+
+def mlstm_chunks_takes(proj: torch.Tensor, dim: int, v_dim: int) -> bool:
+    """Does the chunked form of the matrix memory take this projection (bfloat16, sizes of 64 or 128, rows and the q, k, v
+    parts at whole 16-byte words)?"""
+    return (proj.dtype == torch.bfloat16 and bool(lib().ptb_mlstm_chunks_supports(dim, v_dim))
+            and proj.data_ptr() % 16 == 0 and proj.stride(0) % 8 == 0 and (2 * dim) % 8 == 0)
+
+
 def mlstm(proj: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
           state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, heads: int, dim: int, v_dim: int,
-          q_scale: float) -> torch.Tensor:
+          q_scale: float, chunks=None) -> torch.Tensor:
     """The matrix memory with exponential gates over the step's tokens, continuing and leaving each sequence's state.
     ``proj`` [tokens, >= 2 heads dim + heads v_dim] holds q, k, v side by side (rows may lie wider apart); ``gates``
     float32 [tokens, 2 heads] holds the input and forget gates' projections and is overwritten with the gates'
     logarithms ``cap tanh((g + b) / cap)`` and ``logsigmoid`` of the same; ``state`` [slots, >= mlstm_state_floats]
-    float32. Returns float32 [tokens, heads * v_dim]: S^T q / (max(|n . q|, exp(-m)) + 1e-6)."""
+    float32. ``chunks``: (chunk_seq, chunk_q0, seq_chunk0, n_chunks) for the chunked form on the tensor cores (prompts;
+    ``mlstm_chunks_takes`` says whether it takes the projection), None for the token-by-token form. Returns float32
+    [tokens, heads * v_dim]: S^T q / (max(|n . q|, exp(-m)) + 1e-6)."""
     _need_cuda(gates, bias_i, bias_f, slots)
     _check_rows(proj, proj.shape, proj.dtype, "mlstm: proj")
     n = proj.shape[0]
@@ -1260,6 +1286,19 @@ def mlstm(proj: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor, bias_f:
     _check(lib().ptb_mlstm_gates(_ptr(gates), _ptr(bias_i), _ptr(bias_f), n, heads, ctypes.c_float(cap), _stream(gates)),
            "mlstm_gates")
     out = torch.empty((n, heads * v_dim), dtype=torch.float32, device=proj.device)
+    if chunks is not None:
+        if not mlstm_chunks_takes(proj, dim, v_dim):
+            raise KernelError("mlstm: the chunked form takes bfloat16 projections with keys and values of 64 or 128 entries")
+        chunk_seq, chunk_q0, seq_chunk0, n_chunks = chunks
+        scratch = torch.empty(int(lib().ptb_mlstm_chunks_scratch_floats(n_chunks, heads, dim, v_dim)), dtype=torch.float32,
+                              device=proj.device)
+        _check(lib().ptb_mlstm_chunks(_ptr(proj), proj.stride(0), _ptr(gates), _ptr(state), state.stride(0), _ptr(slots),
+                                      ctypes.byref(batch), _ptr(chunk_seq), _ptr(chunk_q0), _ptr(seq_chunk0), n_chunks,
+                                      _ptr(scratch), _ptr(out), heads, dim, v_dim, ctypes.c_float(q_scale), _stream(proj)),
+               "mlstm_chunks")
+        global launches
+        launches += 2       # three kernels
+        return out
     _check(lib().ptb_mlstm_scan(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(gates), _ptr(state), state.stride(0),
                                 _ptr(slots), ctypes.byref(batch), _ptr(out), heads, dim, v_dim, ctypes.c_float(q_scale),
                                 _stream(proj)), "mlstm_scan")

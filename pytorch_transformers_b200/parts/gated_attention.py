@@ -173,25 +173,45 @@ class SinkAttention(Part):
         else:
             q = res
         tiles = ctx.plan(AttentionTiles.plan_key)
+        gate = proj[:, self.in_rows() - H:] if self.has_gate else None
+        if self.talk and out_scale != 1.0:
+            raise ValueError("sink_attention: mixed softmax weights take no output factor")
+        if (q.dtype == torch.bfloat16 and d == vd and k.attention_mma_supports(d) and out.stride(0) % 2 == 0
+                and out.data_ptr() % 4 == 0):
+            # the tensor-core kernel, tiled as in forward_projected; with mixed weights a block forms one K/V group's
+            # weights on one K/V head's values, float32, and talk_mix sums them
+            tokens, q_per_kv = tiles.facts["mma_tokens"], H // G
+            if tokens == 1:
+                hpk = min(q_per_kv, 128)
+                warps, splits = (hpk + 15) // 16, self._decode_splits(ctx, hpk, G if self.talk else 1)
+            else:
+                warps, splits = 8, 1
+                hpk = max(1, min(q_per_kv, 128 // tokens))
+            margs = (q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"], tiles.facts["n_mma_tiles"], None,
+                     G, self.scale, self.window, tokens, hpk, warps, splits)
+            if self.talk:
+                k.talk_mix(k.attention_mma(*margs, wide_weights=True, keep_first=self.keep_first, wide=True), self.p_talk,
+                           q.dtype, out=out)
+            else:
+                k.attention_mma(*margs, sinks=self.p_sink, gate=gate, out_scale=out_scale, out=out, wide_weights=True,
+                                keep_first=self.keep_first)
+            return
         args = (q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"], tiles.facts["n_tiles"], None, G,
                 self.scale, self.window)
         if self.talk:
-            if out_scale != 1.0:
-                raise ValueError("sink_attention: mixed softmax weights take no output factor")
             k.talk_mix(k.attention_generic(*args, keep_first=self.keep_first, wide=True), self.p_talk, q.dtype, out=out)
             return
-        gate = proj[:, self.in_rows() - H:] if self.has_gate else None
         k.attention_generic(*args, sinks=self.p_sink, gate=gate, out_scale=out_scale, out=out, keep_first=self.keep_first)
 
-    def _decode_splits(self, ctx, hpk: int) -> int:
+    def _decode_splits(self, ctx, hpk: int, value_heads: int = 1) -> int:
         """Blocks per (sequence, K/V head) in a step of single tokens: enough to fill the device, each with two
-        pages of visible keys at least."""
+        pages of visible keys at least. ``value_heads``: K/V heads whose values each group's weights meet."""
         k = self.build.kernels
         q_per_kv = self.heads // self.kv_heads
-        blocks = ctx.n_seqs * self.kv_heads * ((q_per_kv + hpk - 1) // hpk)
+        blocks = ctx.n_seqs * self.kv_heads * ((q_per_kv + hpk - 1) // hpk) * value_heads
         pages = ctx.pages_hint
         if self.window > 0:
-            pages = min(pages, self.window // k.PAGE + 2)
+            pages = min(pages, self.window // k.PAGE + 2 + (self.keep_first + k.PAGE - 1) // k.PAGE)
         return max(1, min((2 * k.sm_count(self.build.device)) // blocks, pages // 2, 64))
 
     fuses_add = True

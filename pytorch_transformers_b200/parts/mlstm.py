@@ -9,7 +9,9 @@ With ``h`` the mixer's input, per head (``dim`` entries of queries and keys, ``v
     o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
     out = W_o ( rmsnorm per head (o) * gain * sigmoid(W_g h) )
 
-Per sequence the mixer keeps S, n and m in the cache's state area (float32) and needs no pages. The gates'
+Prompts of 256 tokens or more run in chunks of 64 on the tensor cores where the kernel takes the sizes (a chunk's own
+sum, the chunks joined in order, the outputs); shorter steps and decoding run token by token. Both carry the same
+running maximum m. Per sequence the mixer keeps S, n and m in the cache's state area (float32) and needs no pages. The gates'
 projections are a product of their own whose float32 sums stay unrounded; biases, cap, logarithms, decays, state,
 the division and the heads' norm are float32 whatever the model dtype. q, k, v and the output gate are one product.
 """
@@ -21,6 +23,7 @@ import torch
 
 from .base import BuildContext, ParamDecl, Part, PartSpec, StateNeed, register_part
 from .linear import linear
+from .recurrent import SCAN_CHUNK, RecurrenceChunks
 
 
 @register_part("mixer", "mlstm")
@@ -35,6 +38,8 @@ class MatrixMemory(Part):
         self.gate_cap, self.eps, self.has_gate = float(gate_cap), float(eps), bool(gate)
         if not (0 < self.dim <= build.kernels.MLSTM_MAX_DIM):
             raise ValueError(f"the matrix memory's kernel takes keys of 1 to {build.kernels.MLSTM_MAX_DIM} entries, got {dim}")
+        if SCAN_CHUNK != build.kernels.MLSTM_CHUNK:
+            raise ValueError("the chunk planner and the chunked kernel disagree on the chunk's size")
         self.p_in = self.p_gates = self.p_i_b = self.p_f_b = self.p_norm = self.p_o = None
 
     def param_decls(self) -> Dict[str, ParamDecl]:
@@ -59,6 +64,9 @@ class MatrixMemory(Part):
     def state_need(self):
         return StateNeed(self.build.kernels.mlstm_state_floats(self.heads, self.dim, self.vdim))
 
+    def planner(self):
+        return RecurrenceChunks()
+
     def runs_beside(self, ctx) -> bool:
         return False
 
@@ -68,8 +76,12 @@ class MatrixMemory(Part):
         proj = linear(k, x, self.p_in)
         gates = linear(k, x, self.p_gates, wide_out=True)
         state = ctx.state_of(entry, self.state_need().numel)
+        plan, chunks = ctx.plan(RecurrenceChunks.plan_key), None
+        if plan.facts["n_chunks"] and k.mlstm_chunks_takes(proj, d, vd):
+            # a long prompt in bfloat16 with sizes of the tensor-core kernels: chunks of 64 tokens in three passes
+            chunks = (plan.dev["chunk_seq"], plan.dev["chunk_q0"], plan.dev["seq_chunk0"], plan.facts["n_chunks"])
         o = k.mlstm(proj, gates, self.p_i_b, self.p_f_b, self.gate_cap, state, ctx.dev["slots"], ctx.batch_c[0], H, d, vd,
-                    d ** -0.5)
+                    d ** -0.5, chunks)
         gate = proj[:, 2 * H * d + H * vd:] if self.has_gate else None
         y = k.head_norm_gate(o, self.p_norm, gate, H, self.eps, proj.dtype)
         return linear(k, y, self.p_o, add=add)

@@ -176,13 +176,47 @@ def test_matrix_memory_whole_in_portions_and_token_by_token(dtype, m):
             cache.close(s)
 
 
+CHUNKED = [dict(heads=2, dim=64, vdim=64, gate_cap=15.0), dict(heads=1, dim=128, vdim=64, gate_cap=6.0),
+           dict(heads=3, dim=64, vdim=128, gate_cap=9.0), dict(heads=2, dim=128, vdim=128, gate_cap=12.0)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("f_bias", [3.0, -2.0])
+@pytest.mark.parametrize("m", CHUNKED, ids=lambda m: f"{m['heads']}x{m['dim']}x{m['vdim']}")
+def test_matrix_memory_long_prompts_in_chunks(dtype, m, f_bias):
+    """Prompts long enough for the chunked form (bfloat16, sizes of the tensor cores) of unequal lengths, whole, cut at
+    and off the chunks' edges, continued from a state that single tokens or an earlier portion left, with forget gates
+    mostly open and mostly closed."""
+    width = 40
+    w = memory_weights(m, width, seed=m["dim"] + m["vdim"], f_bias=f_bias)
+    mixer = Mixer(memory_spec(m, width), {kk: v.float() for kk, v in w.items()}, dtype)
+    g = torch.Generator().manual_seed(2)
+    xs = [bf16_exact(torch.randn(n, width, generator=g)) for n in (700, 333)]
+    refs = [plain.mlstm(x, w, "mix.", m, 1e-5) for x in xs]
+    cache = mixer.cache(64, max_slots=2)
+    for cuts in ([(700, 333)], [(300, 0), (400, 333)], [(256, 5), (1, 1), (443, 327)], [(3, 0), (1, 0), (321, 257), (375, 76)]):
+        slots = [cache.open(), cache.open()]
+        at, got = [0, 0], [[], []]
+        for cut in cuts:
+            live = [b for b in (0, 1) if cut[b] > 0]
+            outs = mixer.step(cache, [slots[b] for b in live], [xs[b][at[b]:at[b] + cut[b]] for b in live])
+            for b, o in zip(live, outs):
+                got[b].append(o)
+                at[b] += cut[b]
+        for b in (0, 1):
+            close(torch.cat(got[b]), refs[b][:at[b]], dtype, f"memory in chunks, cuts {cuts[:3]}", bf16=2.5e-2)
+        for s in slots:
+            cache.close(s)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far,steps", [(0, "prompt"), (3, "tokens"), (63, "prompt"), (64, "tokens")])
-def test_matrix_memory_carries_a_far_key_only_while_the_forget_gate_is_open(dtype, far, steps):
+@pytest.mark.parametrize("d,vd", [(16, 12), (64, 64)])
+def test_matrix_memory_carries_a_far_key_only_while_the_forget_gate_is_open(dtype, far, steps, d, vd):
     """One token long ago has a wide-open input gate and a key that the last query is aligned with. The head whose
     forget gate stays open (bias +8) answers with that token's value; the head whose forget gate closes a little
     every step (bias -1) has lost it among the later tokens."""
-    m, width, T = dict(heads=2, dim=16, vdim=12, gate_cap=12.0), 40, 400
+    m, width, T = dict(heads=2, dim=d, vdim=vd, gate_cap=12.0), 40, 400
     w = memory_weights(m, width, seed=7)
     for name in ("mix.i", "mix.f"):
         w[name] = torch.zeros_like(w[name])
@@ -209,7 +243,7 @@ def test_matrix_memory_carries_a_far_key_only_while_the_forget_gate_is_open(dtyp
     ref = plain.mlstm(x, w, "mix.", m, 1e-5)
     close(got[-1:], ref[-1:], dtype, "last token", f32=3e-5, bf16=4e-2)
     # what the memory gave before the output projection, per head, against the far token's value
-    H, d, vd = 2, 16, 12
+    H = 2
     k_far, q_last = (x[far] @ w["mix.k"].T).view(H, d), (x[T - 1] @ w["mix.q"].T).view(H, d)
     assert (k_far * q_last).sum(-1).abs().min() > 3          # aligned in both heads
     i, f = plain.log_gates(x, w, "mix.", 12.0)
