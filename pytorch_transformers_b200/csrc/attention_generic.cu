@@ -286,6 +286,16 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
   }
 }
 
+// two neighbouring entries in one access (the address a whole pair)
+__device__ __forceinline__ float2 load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Separate projections q | k | v side by side in a row of `proj` (rows `stride` apart), an optional bias on all of
 // them (float32, added here in float32), then for every query and key head: rotation of the first 2 rot_pairs
@@ -301,7 +311,7 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
                                        const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int rot_pairs,
                                        int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm,
                                        const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ lam,
-                                       T* __restrict__ v_keep, int write_cache) {
+                                       T* __restrict__ v_keep, int write_cache, int pairs) {
   extern __shared__ float rows[];   // a row of `dim` floats per warp
   const int t = blockIdx.x;
   const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
@@ -315,7 +325,15 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
     const T* src = row + size_t(hh) * dim;
     const float* bsrc = bias ? bias + size_t(hh) * dim : nullptr;
     T* dst = is_q ? q_out + (size_t(t) * heads + hh) * dim : k_pool + kv_offset(page, hh - heads, in_page, kv_heads, dim);
-    for (int e = lane; e < dim; e += 32) buf[e] = to_f(src[e]) + (bsrc ? bsrc[e] : 0.f);
+    if (pairs) {      // two entries a load (dim even, rows at whole pairs)
+      for (int e = 2 * lane; e < dim; e += 64) {
+        const float2 x = load_pair(src + e);
+        buf[e] = x.x + (bsrc ? bsrc[e] : 0.f);
+        buf[e + 1] = x.y + (bsrc ? bsrc[e + 1] : 0.f);
+      }
+    } else {
+      for (int e = lane; e < dim; e += 32) buf[e] = to_f(src[e]) + (bsrc ? bsrc[e] : 0.f);
+    }
     __syncwarp();
     for (int i = lane; i < rot_pairs; i += 32) {
       const float c = rope_cos[size_t(t) * rot_pairs + i], s = rope_sin[size_t(t) * rot_pairs + i];
@@ -331,7 +349,11 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
       for (int e = lane; e < dim; e += 32) ss = fmaf(buf[e], buf[e], ss);
       rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
     }
-    for (int e = lane; e < dim; e += 32) dst[e] = from_f<T>(buf[e] * rstd);
+    if (pairs) {
+      for (int e = 2 * lane; e < dim; e += 64) store_pair(dst + e, buf[e] * rstd, buf[e + 1] * rstd);
+    } else {
+      for (int e = lane; e < dim; e += 32) dst[e] = from_f<T>(buf[e] * rstd);
+    }
     __syncwarp();
   }
   const T* vsrc = row + size_t(heads + kv_heads) * dim;
@@ -361,6 +383,48 @@ __global__ void talk_mix_kernel(const float* __restrict__ wide, const float* __r
   float acc = 0.f;
   for (int g = 0; g < heads; ++g) acc = fmaf(talk[size_t(h) * heads + g], src[size_t(g) * kv_heads * v_dim], acc);
   out[size_t(t) * out_stride + size_t(h) * v_dim + e] = from_f<T>(acc);
+}
+
+// The same with four value columns a thread and all heads of a K/V group in it: what every head's weights gave on the
+// group's values is read once (16-byte loads) and meets the group's rows of `talk` in registers, eight heads at a time.
+template <typename T>
+__global__ void talk_mix_vec_kernel(const float* __restrict__ wide, const float* __restrict__ talk, T* __restrict__ out,
+                                    int out_stride, long long total, int heads, int kv_heads, int v_dim) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int quads = v_dim / 4, qpk = heads / kv_heads;
+  const int e = int(i % quads) * 4, c = int((i / quads) % kv_heads);
+  const long long t = i / (quads * (long long)kv_heads);
+  const float* src = wide + (size_t(t) * heads * kv_heads + c) * v_dim + e;
+  for (int h0 = 0; h0 < qpk; h0 += 8) {
+    float4 acc[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* trow = talk + size_t(c * qpk + h0) * heads;
+    for (int g = 0; g < heads; ++g) {
+      const float4 v = *reinterpret_cast<const float4*>(src + size_t(g) * kv_heads * v_dim);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (h0 + u < qpk) {
+          const float w = trow[size_t(u) * heads + g];
+          acc[u].x = fmaf(w, v.x, acc[u].x);
+          acc[u].y = fmaf(w, v.y, acc[u].y);
+          acc[u].z = fmaf(w, v.z, acc[u].z);
+          acc[u].w = fmaf(w, v.w, acc[u].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (h0 + u < qpk) {
+        T* dst = out + size_t(t) * out_stride + size_t(c * qpk + h0 + u) * v_dim + e;
+        dst[0] = from_f<T>(acc[u].x);
+        dst[1] = from_f<T>(acc[u].y);
+        dst[2] = from_f<T>(acc[u].z);
+        dst[3] = from_f<T>(acc[u].w);
+      }
+    }
+  }
 }
 
 template <typename T>
@@ -469,15 +533,20 @@ PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const f
   const int threads = 256;
   const size_t smem = size_t(threads / 32) * dim * sizeof(float);
   if (smem > 48 * 1024) return PTB_ERR_SIZE;
+  const size_t pair_bytes = dtype == PTB_F32 ? 8 : 4;
+  const int pairs = (dim % 2 == 0 && stride % 2 == 0 && reinterpret_cast<uintptr_t>(proj) % pair_bytes == 0 &&
+                     reinterpret_cast<uintptr_t>(q_out) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(k_pool) % pair_bytes == 0)
+                        ? 1 : 0;
   if (dtype == PTB_F32)
     rope_norm_store_kernel<float><<<sb->n_tokens, threads, smem, stream>>>(
         (const float*)proj, stride, bias, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, rope_cos, rope_sin, rot_pairs,
-        heads, kv_heads, dim, v_dim, eps, unit_norm, (const float*)v_first, v_first_stride, lam, (float*)v_keep, write_cache);
+        heads, kv_heads, dim, v_dim, eps, unit_norm, (const float*)v_first, v_first_stride, lam, (float*)v_keep, write_cache,
+        pairs);
   else if (dtype == PTB_BF16)
     rope_norm_store_kernel<__nv_bfloat16><<<sb->n_tokens, threads, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, bias, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
         rope_cos, rope_sin, rot_pairs, heads, kv_heads, dim, v_dim, eps, unit_norm, (const __nv_bfloat16*)v_first,
-        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache);
+        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache, pairs);
   else
     return PTB_ERR_DTYPE;
   return launch_status();
@@ -487,6 +556,18 @@ PTB_API int ptb_talk_mix(int dtype, const float* wide, const float* talk, void* 
                          int kv_heads, int v_dim, cudaStream_t stream) {
   if (n_tokens <= 0) return PTB_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || v_dim <= 0 || out_stride < heads * v_dim) return PTB_ERR_SIZE;
+  if (v_dim % 4 == 0 && aligned16(wide)) {
+    const long long total = (long long)n_tokens * kv_heads * (v_dim / 4);
+    const unsigned blocks = unsigned((total + 127) / 128);
+    if (dtype == PTB_F32)
+      talk_mix_vec_kernel<float><<<blocks, 128, 0, stream>>>(wide, talk, (float*)out, out_stride, total, heads, kv_heads, v_dim);
+    else if (dtype == PTB_BF16)
+      talk_mix_vec_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(wide, talk, (__nv_bfloat16*)out, out_stride, total, heads,
+                                                                     kv_heads, v_dim);
+    else
+      return PTB_ERR_DTYPE;
+    return launch_status();
+  }
   const long long total = (long long)n_tokens * heads * v_dim;
   const unsigned blocks = unsigned((total + 255) / 256);
   if (dtype == PTB_F32)

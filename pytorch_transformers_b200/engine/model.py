@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels as K
 from ..cache.paged import Cache
-from ..parts.base import BuildContext, ModelSpec, ParamDecl, Part, make_part, resolve
+from ..parts.base import BuildContext, DeferredSum, ModelSpec, ParamDecl, Part, make_part, resolve
 from ..parts.linear import linear
 from .batch import StepContext, StepError
 
@@ -394,9 +394,18 @@ class CausalLM:
             # the block that runs next, for blocks that can form its opening norm in their own last kernel
             ctx.next_block = self.blocks[self.schedule[i + 1].block] if i + 1 < len(self.schedule) else None
             x = self.blocks[entry.block].forward(x, ctx, entry)   # a tensor, a DeferredSum of two branches or a NormedStream
-        x = resolve(k, x)
         if ctx.n_wanted == 0:
+            if isinstance(x, DeferredSum):
+                x.join(x.base.device)
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        if (isinstance(x, DeferredSum) and hasattr(self.final_norm, "forward_pending") and x.base.dtype == torch.float32
+                and x.pending.dtype == torch.float32):
+            # the last sum only at the wanted rows, in the final norm's kernel
+            x.join(x.base.device)
+            rows, _ = self.final_norm.forward_pending(k.gather_rows(ctx.dev["logits_at"], x.base, self.status),
+                                                      k.gather_rows(ctx.dev["logits_at"], x.pending, self.status), x.bias)
+            return self.logits(rows)
+        x = resolve(k, x)
         rows = k.gather_rows(ctx.dev["logits_at"], x, self.status)
         rows = self.final_norm.forward(rows)
         return self.logits(rows)

@@ -1223,13 +1223,26 @@ DYT_MAX_TAPS = 8
 
 def dyt(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
         conv: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
-        batch: Optional[StepBatchC] = None, single_tokens: bool = False) -> torch.Tensor:
+        batch: Optional[StepBatchC] = None, single_tokens: bool = False, pending: Optional[torch.Tensor] = None,
+        pending_bias: Optional[torch.Tensor] = None):
     """h = tanh(alpha x) * weight + bias, elementwise in float32 (``alpha``: one float32 on the device), written in
     ``out_dtype``. With ``conv`` (float32 [width, taps]) the result is h_t + sum_j conv[:, j] h_(t - taps + 1 + j) over
     each sequence's tokens; the last ``taps - 1`` rows of h per sequence are read from and left in ``state``
-    [slots, >= (taps - 1) width] (float32; rows may lie wider apart)."""
-    _need_cuda(x, alpha, weight, bias, conv, slots)
+    [slots, >= (taps - 1) width] (float32; rows may lie wider apart). With ``pending`` (float32 [n, width], beside a
+    float32 ``x``; ``pending_bias`` float32 [width] or None) the rows are x + (pending + pending_bias): the sum is
+    formed on the way and returned too, as (result, sum)."""
+    _need_cuda(x, alpha, weight, bias, conv, slots, pending, pending_bias)
     n, width = x.shape
+    total = None
+    if pending is not None:
+        if x.dtype != torch.float32 or pending.dtype != torch.float32 or tuple(pending.shape) != (n, width) \
+                or not x.is_contiguous() or not pending.is_contiguous():
+            raise KernelError("dyt: a pending addend is float32 [n, width] beside a float32 x, both contiguous")
+        if pending_bias is not None and (pending_bias.dtype != torch.float32 or pending_bias.numel() != width):
+            raise KernelError("dyt: the pending addend's bias is float32 [width]")
+        total = torch.empty_like(x)
+    elif pending_bias is not None:
+        raise KernelError("dyt: a bias of the pending addend without the addend")
     if alpha.dtype != torch.float32 or alpha.numel() != 1 or weight.dtype != torch.float32 or weight.numel() != width:
         raise KernelError("dyt: alpha is one float32, the weight float32 [width]")
     y = torch.empty((n, width), dtype=out_dtype, device=x.device)
@@ -1244,8 +1257,8 @@ def dyt(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: Option
     _check(lib().ptb_dyt(_dtype_code(x), _ptr(x), _ptr(alpha), _ptr(weight), _ptr(bias), _dtype_code(y), _ptr(y), n, width,
                          _ptr(conv), _ptr(state if taps > 1 else None), 0 if state is None or taps <= 1 else state.stride(0),
                          _ptr(slots), ctypes.byref(batch) if batch is not None else None, taps, 1 if single_tokens else 0,
-                         _stream(x)), "dyt")
-    return y
+                         _ptr(pending), _ptr(pending_bias), _ptr(total), _stream(x)), "dyt")
+    return y if pending is None else (y, total)
 
 
 MLSTM_MAX_DIM = 256   # ptb_mlstm_max_dim()

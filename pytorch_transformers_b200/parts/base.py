@@ -157,10 +157,12 @@ class DeferredSum:
     """A residual stream whose last addition has not been done yet: the value is ``base + pending``.
     A block may hand this to the next block instead of a tensor when ``pending`` is still being
     computed on ``stream``; whoever needs the value waits for that stream and adds (the next
-    block's norm does both in its own kernel). ``resolve`` gives the plain tensor."""
+    block's norm does both in its own kernel). ``resolve`` gives the plain tensor. ``bias`` ([width] float32 or None)
+    is still to be added to ``pending`` (the bias of the product that ``pending`` is the float32 sums of)."""
     base: Any
     pending: Any
     stream: Any = None
+    bias: Any = None
 
     def join(self, device) -> None:
         if self.stream is not None:
@@ -184,7 +186,12 @@ def resolve(kernels, x):
         return x.stream
     if isinstance(x, DeferredSum):
         x.join(x.base.device)
-        return kernels.residual(x.base, x.pending)
+        pending = x.pending
+        if x.bias is not None:      # on a copy: the DeferredSum stays what it was
+            pending = kernels.bias_act_(pending.clone(), x.bias, "none")
+        if x.base.dtype == torch.float32:
+            return kernels.add_stream(x.base, pending)
+        return kernels.residual(x.base, pending)
     return x
 
 

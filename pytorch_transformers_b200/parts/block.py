@@ -96,8 +96,34 @@ class SequentialBlock(Part):
         self.feed_forward = self.children.get("feed_forward")
         self.norm_ff = self.children["norm_ff"] if self.feed_forward is not None else None
 
+    def _defers(self, x) -> bool:
+        """Elementwise norms on a float32 stream, under a mixer and a feed-forward that can leave their last sum to the
+        next norm's kernel: no sum of this block is a kernel of its own."""
+        import torch
+        fuses = getattr(self.mixer, "fuses_norm", None)
+        base = x.base if isinstance(x, DeferredSum) else x
+        return (fuses is not None and fuses(self.norm_mixer) and getattr(self.mixer, "defers_sums", lambda: False)()
+                and torch.is_tensor(base) and base.dtype == torch.float32
+                and (self.feed_forward is None or (hasattr(self.norm_ff, "forward_pending")
+                                                   and hasattr(self.feed_forward, "forward_pending"))))
+
     def forward(self, x, ctx, entry):
         k = self.build.kernels
+        if self._defers(x):
+            # stream + (what the block before left) is formed by the opening norm's kernel, stream + mixer by the
+            # feed-forward's norm, and stream + feed-forward is left to the next block (or the model's end)
+            pending = bias = None
+            if isinstance(x, DeferredSum) and x.pending.dtype == x.base.dtype:
+                x.join(x.base.device)
+                x, pending, bias = x.base, x.pending, x.bias
+            else:
+                x = resolve(k, x)
+            x, mixed, mixed_bias = self.mixer.forward_stream_pending(x, self.norm_mixer, ctx, entry, pending, bias)
+            if self.feed_forward is None:
+                return DeferredSum(x, mixed, bias=mixed_bias)
+            normed, r = self.norm_ff.forward_pending(x, mixed, mixed_bias)
+            out, out_bias = self.feed_forward.forward_pending(normed, ctx)
+            return DeferredSum(r, out, bias=out_bias)
         x = resolve(k, x)
         fuses = getattr(self.mixer, "fuses_norm", None)
         if fuses is not None and fuses(self.norm_mixer):

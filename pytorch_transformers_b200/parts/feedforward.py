@@ -6,7 +6,7 @@ from __future__ import annotations
 from typing import Dict
 
 from .base import BuildContext, ParamDecl, Part, PartSpec, register_part
-from .linear import linear
+from .linear import linear, linear_pending
 
 
 @register_part("feed_forward", "dense")
@@ -36,6 +36,12 @@ class DenseFeedForward(Part):
         if callable(add):
             add = add()   # resolved as late as possible: the caller may still be producing it on another stream
         return linear(k, u, self.p_down_weight, self.p_down_bias, add=add)
+
+    def forward_pending(self, x, ctx):
+        """The result as the last product's float32 sums and its bias, for a kernel that adds them to the stream later."""
+        k = self.build.kernels
+        u = linear(k, x, self.p_up_weight, self.p_up_bias, self.activation)
+        return linear_pending(k, u, self.p_down_weight, self.p_down_bias)
 
 
 @register_part("feed_forward", "clamped_glu")

@@ -31,7 +31,7 @@ import torch
 
 from .attention import MAX_HEAD_DIM, AttentionTiles
 from .base import BuildContext, CacheNeed, ParamDecl, Part, PartSpec, register_part
-from .linear import linear
+from .linear import linear, linear_pending
 
 
 @register_part("mixer", "sink_attention")
@@ -217,8 +217,16 @@ class SinkAttention(Part):
     fuses_add = True
 
     def forward(self, x, ctx, entry, add=None):
+        return linear(self.build.kernels, self._heads(x, ctx, entry), self.p_o, self.p_o_b, add=add)
+
+    def forward_pending(self, x, ctx, entry):
+        """The mixer's result as the last product's float32 sums and its bias, for a kernel that adds them to the
+        stream later."""
+        return linear_pending(self.build.kernels, self._heads(x, ctx, entry), self.p_o, self.p_o_b)
+
+    def _heads(self, x, ctx, entry):
         k = self.build.kernels
         proj = linear(k, x, self.p_in)      # biases, where there are any, are added where q, k, v are laid out
         heads = torch.empty((x.shape[0], self.out_columns()), dtype=x.dtype, device=x.device)
         self.forward_projected(proj, ctx, entry, heads)
-        return linear(k, heads, self.p_o, self.p_o_b, add=add)
+        return heads

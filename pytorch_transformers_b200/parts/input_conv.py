@@ -71,11 +71,26 @@ class InputConvolution(Part):
 
     def forward_stream(self, stream, norm, ctx, entry, add=None):
         """From the un-normed stream: the norm and the convolution in one kernel, then the inner mixer."""
+        return self._run_inner(self._opened(stream, norm, ctx, entry), ctx, entry, add)
+
+    def defers_sums(self) -> bool:
+        return hasattr(self.inner, "forward_pending")
+
+    def forward_stream_pending(self, stream, norm, ctx, entry, pending=None, pending_bias=None):
+        """The same on a float32 stream whose last sum may not be formed yet (stream + (pending + pending_bias)), and
+        without the sum at the end: (the stream as this block read it, the inner mixer's float32 result, its bias)."""
+        if pending is not None:
+            y, stream = self._opened(stream, norm, ctx, entry, pending, pending_bias)
+        else:
+            y = self._opened(stream, norm, ctx, entry)
+        return (stream,) + tuple(self.inner.forward_pending(y, ctx, self._inner_entry(entry)))
+
+    def _opened(self, stream, norm, ctx, entry, pending=None, pending_bias=None):
         k = self.build.kernels
         state = ctx.state_of(entry, self.own_state) if self.own_state else None
-        y = k.dyt(stream, norm.p_alpha, norm.p_weight, norm.p_bias, norm.out_dtype(stream), conv=self.p_conv, state=state,
-                  slots=ctx.dev["slots"], batch=ctx.batch_c[0], single_tokens=ctx.is_decode)
-        return self._run_inner(y, ctx, entry, add)
+        return k.dyt(stream, norm.p_alpha, norm.p_weight, norm.p_bias, norm.out_dtype(stream), conv=self.p_conv, state=state,
+                     slots=ctx.dev["slots"], batch=ctx.batch_c[0], single_tokens=ctx.is_decode, pending=pending,
+                     pending_bias=pending_bias)
 
     def forward(self, x, ctx, entry, add=None):
         """From an input that is normed already."""

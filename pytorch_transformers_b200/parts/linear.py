@@ -23,6 +23,14 @@ import torch
 TC_LINEAR_ROWS = None
 
 
+def linear_pending(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """A product whose result is to be added to a float32 stream by a later kernel: (the float32 sums unrounded, the
+    bias that is still to be added or None when it is in already)."""
+    if weight.dtype == torch.float32:
+        return kernels.linear_f32(x, weight, bias, "none"), None
+    return linear(kernels, x, weight, wide_out=True), bias
+
+
 def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            act: str = "none", add: Optional[torch.Tensor] = None, wide_out: bool = False) -> torch.Tensor:
     """act(x @ weight.T + bias) + add, in the model dtype; ``add`` has the result's shape. ``wide_out``: a plain

@@ -22,7 +22,7 @@ from typing import Dict
 import torch
 
 from .base import BuildContext, ParamDecl, Part, PartSpec, StateNeed, register_part
-from .linear import linear
+from .linear import linear, linear_pending
 from .recurrent import SCAN_CHUNK, RecurrenceChunks
 
 
@@ -71,6 +71,13 @@ class MatrixMemory(Part):
         return False
 
     def forward(self, x, ctx, entry, add=None):
+        return linear(self.build.kernels, self._heads(x, ctx, entry), self.p_o, add=add)
+
+    def forward_pending(self, x, ctx, entry):
+        """The mixer's result as the last product's float32 sums, for a kernel that adds them to the stream later."""
+        return linear_pending(self.build.kernels, self._heads(x, ctx, entry), self.p_o)
+
+    def _heads(self, x, ctx, entry):
         k = self.build.kernels
         H, d, vd = self.heads, self.dim, self.vdim
         proj = linear(k, x, self.p_in)
@@ -83,5 +90,4 @@ class MatrixMemory(Part):
         o = k.mlstm(proj, gates, self.p_i_b, self.p_f_b, self.gate_cap, state, ctx.dev["slots"], ctx.batch_c[0], H, d, vd,
                     d ** -0.5, chunks)
         gate = proj[:, 2 * H * d + H * vd:] if self.has_gate else None
-        y = k.head_norm_gate(o, self.p_norm, gate, H, self.eps, proj.dtype)
-        return linear(k, y, self.p_o, add=add)
+        return k.head_norm_gate(o, self.p_norm, gate, H, self.eps, proj.dtype)

@@ -109,3 +109,9 @@ class DynamicTanh(Part):
 
     def forward(self, x):
         return self.build.kernels.dyt(x, self.p_alpha, self.p_weight, self.p_bias, self.out_dtype(x))
+
+    def forward_pending(self, base, pending, pending_bias=None):
+        """The norm of base + (pending + pending_bias), float32 rows that have not been summed yet: (normed, sum), both
+        out of one kernel."""
+        return self.build.kernels.dyt(base, self.p_alpha, self.p_weight, self.p_bias, self.out_dtype(base), pending=pending,
+                                      pending_bias=pending_bias)

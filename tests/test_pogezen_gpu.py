@@ -465,7 +465,10 @@ def test_residual_stream_after_every_layer(loaded):
         for b in blocks:
             del b.forward
     assert len(got) == len(want) == 5
+    from pytorch_transformers_b200.parts.base import DeferredSum, resolve
+    assert all(isinstance(a, DeferredSum) for a in got)      # no sum is a kernel of its own: the next norm forms it
     for i, (a, b) in enumerate(zip(got, want)):
+        a = resolve(K(), a)
         assert a.dtype == torch.float32 and row_errors(a, b).max() < 1e-5, f"layer {i}"
 
 
