@@ -572,7 +572,7 @@ class KernelTimes:
              "latent_unfolded_attention",
              "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_",
              "embed_sum", "post_norm_add", "qk_norm_store", "linear_attention", "norm_gate", "glu_clamp", "softcap_",
-             "dyt", "mlstm", "head_norm_gate", "rope_norm_store", "talk_mix")
+             "dyt", "mlstm", "head_norm_gate", "rope_norm_store", "talk_mix", "embed_rows")
 
     def __init__(self, kernels):
         self.k, self.records, self.saved = kernels, [], {}
@@ -926,7 +926,12 @@ def run_pogezen(args):
         flops = 2 * tokens * w * (2 * n_mem + 2 * n_att + 4 * 2 * 4 * w)
         roof["library_products_TFLOPs"] = round(flops / t["ms"] / 1e9, 1)
         roof["library_products_frac_of_burst"] = round(roof["library_products_TFLOPs"] / pk["bf16_tflops"], 4)
-    for key, bytes_per_row in (("dyt", w * (4 + 2)), ("head_norm_gate", mh * mv * (4 + 2 + 2)),
+    # the norm kernels of a prompt: the first reads the stream and writes normed rows (4 + 2 bytes a column), the others
+    # also read the float32 sums still to be added and write the new stream (4 + 4 + 4 + 2); the last norms one row
+    norms = sum(2 if layer["mlp"] is not None else 1 for layer in raw["layers"])
+    dyt_calls = G["prefill_kernels_ms"].get("dyt", {}).get("calls", norms + 1)
+    dyt_row = w * ((4 + 2) + (norms - 1) * (4 + 4 + 4 + 2)) / dyt_calls
+    for key, bytes_per_row in (("dyt", dyt_row), ("head_norm_gate", mh * mv * (4 + 2 + 2)),
                                ("rope_norm_store", ((H + K) * d + K * vd) * 4), ("talk_mix", H * vd * (4 * K + 2)),
                                ("mlstm_gates", 0)):
         t = per_call(G["prefill_kernels_ms"], key)

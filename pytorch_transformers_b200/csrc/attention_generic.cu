@@ -304,7 +304,9 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
 // root, no gain). Values: v <- (1 - lam) v + lam v_first with the values of the same token that an earlier layer
 // kept (`v_first`, rows v_first_stride apart; lam one float32 on the device); `v_keep` receives this layer's own
 // values (with bias, before any mixing) for later layers. Keys and values go into the paged pools at the tokens'
-// positions, queries to q_out [tokens, heads, dim]. One block per token, a warp per head.
+// positions, queries to q_out [tokens, heads, dim]. A warp per (token, head): query heads, then key heads, then the
+// K/V heads' values; the warps of a block share nothing, so a head's chain of loads, rotation, sum and stores waits
+// for no other.
 template <typename T>
 __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, const float* __restrict__ bias,
                                        T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool, StepBatch sb,
@@ -312,59 +314,77 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
                                        int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm,
                                        const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ lam,
                                        T* __restrict__ v_keep, int write_cache, int pairs) {
-  extern __shared__ float rows[];   // a row of `dim` floats per warp
-  const int t = blockIdx.x;
-  const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
-  const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE], in_page = pos % PTB_PAGE;
+  extern __shared__ float rows[];   // per warp: a row of `dim` floats, then cos and sin of the rotated pairs
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int units = heads + 2 * kv_heads;
+  const long long u = (long long)blockIdx.x * (blockDim.x / 32) + warp;
+  if (u >= (long long)sb.n_tokens * units) return;
+  const int t = int(u / units), hh = int(u % units);
   const T* row = proj + size_t(t) * stride;
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, n_warps = blockDim.x / 32;
-  float* buf = rows + size_t(warp) * dim;
-  for (int hh = warp; hh < heads + kv_heads; hh += n_warps) {
-    const bool is_q = hh < heads;
-    if (!is_q && !write_cache) continue;
-    const T* src = row + size_t(hh) * dim;
-    const float* bsrc = bias ? bias + size_t(hh) * dim : nullptr;
-    T* dst = is_q ? q_out + (size_t(t) * heads + hh) * dim : k_pool + kv_offset(page, hh - heads, in_page, kv_heads, dim);
-    if (pairs) {      // two entries a load (dim even, rows at whole pairs)
-      for (int e = 2 * lane; e < dim; e += 64) {
-        const float2 x = load_pair(src + e);
-        buf[e] = x.x + (bsrc ? bsrc[e] : 0.f);
-        buf[e + 1] = x.y + (bsrc ? bsrc[e + 1] : 0.f);
-      }
-    } else {
-      for (int e = lane; e < dim; e += 32) buf[e] = to_f(src[e]) + (bsrc ? bsrc[e] : 0.f);
+  if (hh >= heads + kv_heads) {     // the values of one K/V head
+    const int g = hh - heads - kv_heads;
+    const T* vsrc = row + size_t(heads + kv_heads) * dim + size_t(g) * v_dim;
+    const float* vb = bias ? bias + size_t(heads + kv_heads) * dim + size_t(g) * v_dim : nullptr;
+    const float l = (v_first != nullptr) ? lam[0] : 0.f;
+    T* dst = nullptr;
+    if (write_cache) {
+      const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
+      const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE];
+      dst = v_pool + kv_offset(page, g, pos % PTB_PAGE, kv_heads, v_dim);
     }
-    __syncwarp();
-    for (int i = lane; i < rot_pairs; i += 32) {
-      const float c = rope_cos[size_t(t) * rot_pairs + i], s = rope_sin[size_t(t) * rot_pairs + i];
-      float a, b;
-      rotate_pair(buf[i], buf[i + rot_pairs], c, s, a, b);
-      buf[i] = a;
-      buf[i + rot_pairs] = b;
+    for (int e = lane; e < v_dim; e += 32) {
+      float v = to_f(vsrc[e]) + (vb ? vb[e] : 0.f);
+      if (v_keep) v_keep[(size_t(t) * kv_heads + g) * v_dim + e] = from_f<T>(v);
+      if (v_first != nullptr) v = (1.f - l) * round_store<T>(v) + l * to_f(v_first[size_t(t) * v_first_stride + size_t(g) * v_dim + e]);
+      if (dst) dst[e] = from_f<T>(v);
     }
-    __syncwarp();
-    float rstd = 1.f;
-    if (unit_norm) {
-      float ss = 0.f;
-      for (int e = lane; e < dim; e += 32) ss = fmaf(buf[e], buf[e], ss);
-      rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
-    }
-    if (pairs) {
-      for (int e = 2 * lane; e < dim; e += 64) store_pair(dst + e, buf[e] * rstd, buf[e + 1] * rstd);
-    } else {
-      for (int e = lane; e < dim; e += 32) dst[e] = from_f<T>(buf[e] * rstd);
-    }
-    __syncwarp();
+    return;
   }
-  const T* vsrc = row + size_t(heads + kv_heads) * dim;
-  const float* vb = bias ? bias + size_t(heads + kv_heads) * dim : nullptr;
-  const float l = (v_first != nullptr) ? lam[0] : 0.f;
-  for (int i = threadIdx.x; i < kv_heads * v_dim; i += blockDim.x) {
-    const int g = i / v_dim, e = i % v_dim;
-    float v = to_f(vsrc[i]) + (vb ? vb[i] : 0.f);
-    if (v_keep) v_keep[size_t(t) * kv_heads * v_dim + i] = from_f<T>(v);
-    if (v_first != nullptr) v = (1.f - l) * round_store<T>(v) + l * to_f(v_first[size_t(t) * v_first_stride + i]);
-    if (write_cache) v_pool[kv_offset(page, g, in_page, kv_heads, v_dim) + e] = from_f<T>(v);
+  const bool is_q = hh < heads;
+  if (!is_q && !write_cache) return;
+  float* buf = rows + size_t(warp) * (dim + 2 * rot_pairs);
+  float* cs = buf + dim;
+  const T* src = row + size_t(hh) * dim;
+  const float* bsrc = bias ? bias + size_t(hh) * dim : nullptr;
+  T* dst;
+  if (is_q) {
+    dst = q_out + (size_t(t) * heads + hh) * dim;
+  } else {
+    const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
+    const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE];
+    dst = k_pool + kv_offset(page, hh - heads, pos % PTB_PAGE, kv_heads, dim);
+  }
+  for (int i = lane; i < rot_pairs; i += 32) {       // issued with the row's loads
+    cs[i] = rope_cos[size_t(t) * rot_pairs + i];
+    cs[rot_pairs + i] = rope_sin[size_t(t) * rot_pairs + i];
+  }
+  if (pairs) {      // two entries a load (dim even, rows at whole pairs)
+    for (int e = 2 * lane; e < dim; e += 64) {
+      const float2 x = load_pair(src + e);
+      buf[e] = x.x + (bsrc ? bsrc[e] : 0.f);
+      buf[e + 1] = x.y + (bsrc ? bsrc[e + 1] : 0.f);
+    }
+  } else {
+    for (int e = lane; e < dim; e += 32) buf[e] = to_f(src[e]) + (bsrc ? bsrc[e] : 0.f);
+  }
+  __syncwarp();
+  for (int i = lane; i < rot_pairs; i += 32) {
+    float a, b;
+    rotate_pair(buf[i], buf[i + rot_pairs], cs[i], cs[rot_pairs + i], a, b);
+    buf[i] = a;
+    buf[i + rot_pairs] = b;
+  }
+  __syncwarp();
+  float rstd = 1.f;
+  if (unit_norm) {
+    float ss = 0.f;
+    for (int e = lane; e < dim; e += 32) ss = fmaf(buf[e], buf[e], ss);
+    rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+  }
+  if (pairs) {
+    for (int e = 2 * lane; e < dim; e += 64) store_pair(dst + e, buf[e] * rstd, buf[e + 1] * rstd);
+  } else {
+    for (int e = lane; e < dim; e += 32) dst[e] = from_f<T>(buf[e] * rstd);
   }
 }
 
@@ -530,20 +550,22 @@ PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const f
       rot_pairs < 0 || 2 * rot_pairs > dim || (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) ||
       (v_first != nullptr && lam == nullptr) || dim > 4096)
     return PTB_ERR_SIZE;
-  const int threads = 256;
-  const size_t smem = size_t(threads / 32) * dim * sizeof(float);
+  const int warps = 8, threads = 32 * warps;
+  const size_t smem = size_t(warps) * (dim + 2 * size_t(rot_pairs)) * sizeof(float);
   if (smem > 48 * 1024) return PTB_ERR_SIZE;
+  const long long units = (long long)sb->n_tokens * (heads + 2 * kv_heads);
+  const unsigned blocks = unsigned((units + warps - 1) / warps);
   const size_t pair_bytes = dtype == PTB_F32 ? 8 : 4;
   const int pairs = (dim % 2 == 0 && stride % 2 == 0 && reinterpret_cast<uintptr_t>(proj) % pair_bytes == 0 &&
                      reinterpret_cast<uintptr_t>(q_out) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(k_pool) % pair_bytes == 0)
                         ? 1 : 0;
   if (dtype == PTB_F32)
-    rope_norm_store_kernel<float><<<sb->n_tokens, threads, smem, stream>>>(
+    rope_norm_store_kernel<float><<<blocks, threads, smem, stream>>>(
         (const float*)proj, stride, bias, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, rope_cos, rope_sin, rot_pairs,
         heads, kv_heads, dim, v_dim, eps, unit_norm, (const float*)v_first, v_first_stride, lam, (float*)v_keep, write_cache,
         pairs);
   else if (dtype == PTB_BF16)
-    rope_norm_store_kernel<__nv_bfloat16><<<sb->n_tokens, threads, smem, stream>>>(
+    rope_norm_store_kernel<__nv_bfloat16><<<blocks, threads, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, bias, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
         rope_cos, rope_sin, rot_pairs, heads, kv_heads, dim, v_dim, eps, unit_norm, (const __nv_bfloat16*)v_first,
         v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache, pairs);

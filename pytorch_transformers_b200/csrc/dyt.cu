@@ -139,8 +139,9 @@ __global__ void dyt_vec_kernel(const TI* __restrict__ x, const float* __restrict
 }
 
 // grid (ceil(width / 4 / threads), ceil(tokens / RUN)): a thread walks RUN tokens of the step in order; their inputs
-// are all loaded before the first is used
-template <typename TI, typename TO, int RUN>
+// are all loaded before the first is used. MT: the most taps this instance takes (its registers hold MT weights and
+// MT - 1 earlier inputs of four channels)
+template <typename TI, typename TO, int RUN, int MT>
 __global__ void dyt_conv_vec_kernel(const TI* __restrict__ x, const float* __restrict__ alpha, const float* __restrict__ w,
                                     const float* __restrict__ b, const float* __restrict__ conv, float* __restrict__ state,
                                     int state_stride, const int* __restrict__ slots, StepBatch sb, TO* __restrict__ y,
@@ -153,6 +154,17 @@ __global__ void dyt_conv_vec_kernel(const TI* __restrict__ x, const float* __res
   float4 xv[RUN];
 #pragma unroll
   for (int u = 0; u < RUN; ++u) xv[u] = t0 + u < t1 ? row_value4(x, pd, pb, size_t(t0 + u) * width + c) : zero;
+  // the taps - 1 inputs before the run's first token, oldest first: rows of this step where the sequence has that many
+  // in it, else the slot's state; loaded with the run's own rows, so that the thread waits for memory once
+  const int seq0 = sb.tok_seq[t0], start0 = sb.seq_start[seq0], idx0 = t0 - start0;
+  float4 wraw[MT - 1];
+#pragma unroll
+  for (int j = 0; j < MT - 1; ++j) {
+    if (j >= taps - 1) break;
+    const int src = idx0 - (taps - 1) + j;
+    wraw[j] = (src >= 0) ? row_value4(x, pd, pb, size_t(start0 + src) * width + c)
+                         : load4(state + size_t(slots[seq0]) * state_stride + size_t(taps - 1 + src) * width + c);
+  }
   if (pd.sum_out) {
 #pragma unroll
     for (int u = 0; u < RUN; ++u)
@@ -160,9 +172,9 @@ __global__ void dyt_conv_vec_kernel(const TI* __restrict__ x, const float* __res
   }
   const float a = alpha[0];
   const float4 wc = load4(w + c), bc = b ? load4(b + c) : zero;
-  float4 cw[MAX_TAPS], win[MAX_TAPS - 1];
+  float4 cw[MT], win[MT - 1];
 #pragma unroll
-  for (int j = 0; j < MAX_TAPS; ++j) {
+  for (int j = 0; j < MT; ++j) {
     if (j >= taps) break;
     cw[j] = make_float4(conv[size_t(c) * taps + j], conv[size_t(c + 1) * taps + j], conv[size_t(c + 2) * taps + j],
                         conv[size_t(c + 3) * taps + j]);
@@ -174,35 +186,39 @@ __global__ void dyt_conv_vec_kernel(const TI* __restrict__ x, const float* __res
     const int seq = sb.tok_seq[t], start = sb.seq_start[seq];
     const int idx = t - start;
     float* st = state + size_t(slots[seq]) * state_stride;
-    if (t == t0 || idx == 0) {        // the window of the taps - 1 inputs before this token, oldest first
+    if (t == t0) {                    // the window of the taps - 1 inputs before this token, oldest first
 #pragma unroll
-      for (int j = 0; j < MAX_TAPS - 1; ++j) {
+      for (int j = 0; j < MT - 1; ++j) {
         if (j >= taps - 1) break;
-        const int src = idx - (taps - 1) + j;
-        win[j] = (src >= 0) ? dyt4(row_value4(x, pd, pb, size_t(start + src) * width + c), a, wc, bc)
-                            : load4(st + size_t(taps - 1 + src) * width + c);
+        win[j] = (idx - (taps - 1) + j >= 0) ? dyt4(wraw[j], a, wc, bc) : wraw[j];
+      }
+    } else if (idx == 0) {            // a sequence that starts inside the run: all of its window is its slot's state
+#pragma unroll
+      for (int j = 0; j < MT - 1; ++j) {
+        if (j >= taps - 1) break;
+        win[j] = load4(st + size_t(j) * width + c);
       }
     }
     const float4 own = dyt4(xv[u], a, wc, bc);
     float4 acc = own;
 #pragma unroll
-    for (int j = 0; j < MAX_TAPS - 1; ++j) {
+    for (int j = 0; j < MT - 1; ++j) {
       if (j >= taps - 1) break;
       acc = fma4(cw[j], win[j], acc);
     }
 #pragma unroll
-    for (int j = 0; j < MAX_TAPS; ++j)
+    for (int j = 0; j < MT; ++j)
       if (j == taps - 1) acc = fma4(cw[j], own, acc);
     store4(y + size_t(t) * width + c, acc);
 #pragma unroll
-    for (int j = 0; j < MAX_TAPS - 1; ++j) {      // slide
+    for (int j = 0; j < MT - 1; ++j) {      // slide
       if (j >= taps - 1) break;
-      win[j] = (j + 1 < taps - 1) ? win[j + 1 < MAX_TAPS - 1 ? j + 1 : j] : own;
+      win[j] = (j + 1 < taps - 1) ? win[j + 1 < MT - 1 ? j + 1 : j] : own;
     }
     if (write_state && idx == 0) {
       // every sequence brings one token: the window after the slide is the state
 #pragma unroll
-      for (int j = 0; j < MAX_TAPS - 1; ++j) {
+      for (int j = 0; j < MT - 1; ++j) {
         if (j >= taps - 1) break;
         store4(st + size_t(j) * width + c, win[j]);
       }
@@ -256,12 +272,24 @@ int launch_dyt(const void* x, const float* alpha, const float* w, const float* b
   if (vec) {
     const int vthreads = 128, across = (width / 4 + vthreads - 1) / vthreads;
 #define PTB_DYT_RUN(RUN)                                                                                                  \
-  dyt_conv_vec_kernel<TI, TO, RUN><<<dim3(across, (n + RUN - 1) / RUN), vthreads, 0, stream>>>(                           \
-      (const TI*)x, alpha, w, b, conv, state, state_stride, slots, *sb, (TO*)y, n, width, taps, single_tokens, pd)
-    if (n >= 2048)
+  do {                                                                                                                    \
+    if (taps <= 4)                                                                                                        \
+      dyt_conv_vec_kernel<TI, TO, RUN, 4><<<dim3(across, (n + RUN - 1) / RUN), vthreads, 0, stream>>>(                    \
+          (const TI*)x, alpha, w, b, conv, state, state_stride, slots, *sb, (TO*)y, n, width, taps, single_tokens, pd);   \
+    else                                                                                                                  \
+      dyt_conv_vec_kernel<TI, TO, RUN, MAX_TAPS><<<dim3(across, (n + RUN - 1) / RUN), vthreads, 0, stream>>>(             \
+          (const TI*)x, alpha, w, b, conv, state, state_stride, slots, *sb, (TO*)y, n, width, taps, single_tokens, pd);   \
+  } while (0)
+    // the longest run that still gives every SM a thousand threads: a run of RUN tokens forms RUN + taps - 1 values of
+    // tanh instead of RUN * taps, but a step has to fill the machine first (a run of 8 at 2,048 x 2,048 left it a
+    // fifth occupied and took four times a plain pass)
+    const long long want = 148LL * 1024, lanes = (long long)across * vthreads;
+    if (lanes * ((n + 7) / 8) >= want)
       PTB_DYT_RUN(8);
-    else if (n >= 256)
+    else if (lanes * ((n + 3) / 4) >= want)
       PTB_DYT_RUN(4);
+    else if (lanes * ((n + 1) / 2) >= want)
+      PTB_DYT_RUN(2);
     else
       PTB_DYT_RUN(1);
 #undef PTB_DYT_RUN

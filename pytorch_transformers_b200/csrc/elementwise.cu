@@ -48,6 +48,50 @@ PTB_API int ptb_gather_rows(int dtype, const int* ids, const void* table, void* 
   return launch_status();
 }
 
+// rows of a table into a float32 stream: out[t, :] = float(table[ids[t], :]) * scale, the product formed in float32
+// (what a gather, a widening and a scaling in place give, in one pass). An id out of range as above.
+template <typename T>
+__global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                  int width, int rows, float scale, int* status) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= rows) {
+    if (threadIdx.x == 0 && status) atomicOr(status, 1);
+    id = 0;
+  }
+  const T* src = table + size_t(id) * width;
+  float* dst = out + size_t(t) * width;
+  if (width % 4 == 0 && (reinterpret_cast<uintptr_t>(table) % (4 * sizeof(T)) == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0)) {
+    for (int i = 4 * threadIdx.x; i < width; i += 4 * blockDim.x) {
+      float4 v;
+      if constexpr (sizeof(T) == 4) {
+        v = *reinterpret_cast<const float4*>(src + i);
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(src + i);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        v = make_float4(a.x, a.y, b.x, b.y);
+      }
+      *reinterpret_cast<float4*>(dst + i) = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f(src[i]) * scale;
+  }
+}
+
+PTB_API int ptb_embed_rows(int dtype, const int* ids, const void* table, float* out, int n, int width, int rows, float scale,
+                           int* status, cudaStream_t stream) {
+  if (n <= 0) return PTB_OK;
+  if (width <= 0 || rows <= 0) return PTB_ERR_SIZE;
+  if (dtype == PTB_F32)
+    embed_rows_kernel<float><<<n, 256, 0, stream>>>(ids, (const float*)table, out, width, rows, scale, status);
+  else if (dtype == PTB_BF16)
+    embed_rows_kernel<__nv_bfloat16><<<n, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, rows, scale, status);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
 // ------------------------------------------------------------------------------------------------
 // Normalisation of rows. kind 0: LayerNorm, y = (x - mean) / sqrt(var + eps) * gain + bias with the
 // biased variance; kind 1: RMSNorm, y = x / sqrt(mean(x^2) + eps) * gain (+ bias if given).

@@ -143,16 +143,60 @@ mlstm_chunk_sum_kernel(const __nv_bfloat16* __restrict__ proj, int stride, const
 }
 
 // ------------------------------------------------------------------------------------------------ pass 2
-// One thread per (sequence, head, element of S or of n) walks the sequence's chunks in order: sums[c] and nsums[c]
-// become the state BEFORE chunk c, m_before[c] its running maximum, and the state area receives the state after the
-// last chunk. Every thread follows the head's chain of maxima itself (two numbers a chunk).
-__global__ void mlstm_chunk_join_kernel(float* __restrict__ sums, float* __restrict__ nsums, const float* __restrict__ meta,
-                                        float* __restrict__ m_before, float* __restrict__ state, int state_stride,
-                                        const int* __restrict__ slots, StepBatch sb, const int* __restrict__ seq_chunk0,
-                                        int heads, int dim, int v_dim) {
+// First the heads' chains of maxima, which are two numbers a chunk: a warp per (sequence, head) reads 32 chunks' totals
+// and maxima at a time, follows m_new = max(g + m, g + M) in order (the sums that the token-by-token form makes), and
+// leaves for every chunk the maximum before it (m_before) and, in place of (g, M), the two factors of its join:
+// exp(g + m - m_new) on the state so far and exp(g + M - m_new) on the chunk's own sums. m_after [sequences][heads]
+// receives the maximum after the sequence's last chunk. The state area is only read here.
+__global__ void mlstm_chunk_decay_kernel(float* __restrict__ meta, float* __restrict__ m_before, float* __restrict__ m_after,
+                                         const float* __restrict__ state, int state_stride, const int* __restrict__ slots,
+                                         StepBatch sb, const int* __restrict__ seq_chunk0, int heads, int dim, int v_dim) {
+  const unsigned full = 0xffffffffu;
+  const int seq = blockIdx.y, lane = threadIdx.x & 31;
+  const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (h >= heads) return;
+  const size_t per_S = size_t(dim) * v_dim;
+  const int copies = (v_dim + VB - 1) / VB;
+  const int n_new = sb.seq_new[seq], c0 = seq_chunk0[seq];
+  const int n_chunks = (n_new + CH - 1) / CH;
+  const float* st = state + size_t(slots[seq]) * state_stride;
+  float m = st[size_t(heads) * per_S + size_t(h) * copies * (dim + 1) + dim];
+  for (int g0 = 0; g0 < n_chunks; g0 += 32) {
+    const int c = g0 + lane;
+    const bool ok = c < n_chunks;
+    float* mt = meta + (size_t(c0 + c) * heads + h) * 2;
+    const float tot = ok ? mt[0] : 0.f, mx = ok ? mt[1] : 0.f;
+    float m_prev = 0.f, m_mine = 0.f;
+    const int n_here = min(32, n_chunks - g0);
+    for (int i = 0; i < n_here; ++i) {
+      const float t = __shfl_sync(full, tot, i), x = __shfl_sync(full, mx, i);
+      const float m_new = fmaxf(t + m, t + x);
+      if (lane == i) {
+        m_prev = m;
+        m_mine = m_new;
+      }
+      m = m_new;
+    }
+    if (ok) {
+      m_before[size_t(c0 + c) * heads + h] = m_prev;
+      mt[0] = expf(tot + m_prev - m_mine);
+      mt[1] = expf(tot + mx - m_mine);
+    }
+  }
+  if (lane == 0) m_after[size_t(seq) * heads + h] = m;
+}
+
+// Then the join itself, elementwise: a thread owns four neighbouring elements of one head's S or n and walks the
+// sequence's chunks in order: sums[c] and nsums[c] become the state BEFORE chunk c, and the state area receives the
+// state after the last chunk (with m_after in every copy of m). Eight chunks' own sums are loaded ahead of the chain.
+__global__ void __launch_bounds__(128)
+mlstm_chunk_join_kernel(float* __restrict__ sums, float* __restrict__ nsums, const float* __restrict__ factors,
+                        const float* __restrict__ m_after, float* __restrict__ state, int state_stride,
+                        const int* __restrict__ slots, StepBatch sb, const int* __restrict__ seq_chunk0, int heads, int dim,
+                        int v_dim) {
   const int seq = blockIdx.y;
-  const size_t per_S = size_t(dim) * v_dim, per_head = per_S + dim;
-  const size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t per_S = size_t(dim) * v_dim, per_head = per_S + dim;      // both multiples of 4
+  const size_t e = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (e >= per_head * heads) return;
   const int h = int(e / per_head);
   const size_t r = e % per_head;
@@ -162,38 +206,46 @@ __global__ void mlstm_chunk_join_kernel(float* __restrict__ sums, float* __restr
   const int n_chunks = (n_new + CH - 1) / CH;
   float* st = state + size_t(slots[seq]) * state_stride;
   float* n_area = st + size_t(heads) * per_S + size_t(h) * copies * (dim + 1);     // the head's copies of n and m
-  float* mine = is_n ? n_area + (r - per_S) : st + size_t(h) * per_S + r;
+  float* mine = is_n ? n_area + (r - per_S) : st + size_t(h) * per_S + r;          // at no whole 16-byte word in general
   float* chunked = is_n ? nsums + size_t(h) * dim + (r - per_S) : sums + size_t(h) * per_S + r;
   const size_t chunk_stride = is_n ? size_t(heads) * dim : size_t(heads) * per_S;
-  const bool writes_m = is_n && r == per_S;
-  float s = *mine, m = n_area[dim];
-  constexpr int AHEAD = 8;      // chunks whose own sums are loaded before the chain of updates needs them
+  float4 s = make_float4(mine[0], mine[1], mine[2], mine[3]);
+  constexpr int AHEAD = 8;
   for (int g0 = 0; g0 < n_chunks; g0 += AHEAD) {
-    float own[AHEAD], tot[AHEAD], mx[AHEAD];
+    float4 own[AHEAD];
+    float keep[AHEAD], add[AHEAD];
 #pragma unroll
     for (int i = 0; i < AHEAD; ++i) {
       const bool ok = g0 + i < n_chunks;
-      own[i] = ok ? chunked[size_t(c0 + g0 + i) * chunk_stride] : 0.f;
-      tot[i] = ok ? meta[(size_t(c0 + g0 + i) * heads + h) * 2] : 0.f;
-      mx[i] = ok ? meta[(size_t(c0 + g0 + i) * heads + h) * 2 + 1] : 0.f;
+      own[i] = ok ? *reinterpret_cast<const float4*>(chunked + size_t(c0 + g0 + i) * chunk_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+      keep[i] = ok ? factors[(size_t(c0 + g0 + i) * heads + h) * 2] : 0.f;
+      add[i] = ok ? factors[(size_t(c0 + g0 + i) * heads + h) * 2 + 1] : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < AHEAD; ++i) {
       if (g0 + i >= n_chunks) break;
-      chunked[size_t(c0 + g0 + i) * chunk_stride] = s;
-      if (writes_m) m_before[size_t(c0 + g0 + i) * heads + h] = m;
-      const float m_own = tot[i] + mx[i], m_new = fmaxf(tot[i] + m, m_own);
-      s = fmaf(expf(tot[i] + m - m_new), s, expf(m_own - m_new) * own[i]);
-      m = m_new;
+      *reinterpret_cast<float4*>(chunked + size_t(c0 + g0 + i) * chunk_stride) = s;
+      s.x = fmaf(keep[i], s.x, add[i] * own[i].x);
+      s.y = fmaf(keep[i], s.y, add[i] * own[i].y);
+      s.z = fmaf(keep[i], s.z, add[i] * own[i].z);
+      s.w = fmaf(keep[i], s.w, add[i] * own[i].w);
     }
   }
   if (is_n) {
+    const float m = m_after[size_t(seq) * heads + h];
     for (int z = 0; z < copies; ++z) {
-      n_area[size_t(z) * (dim + 1) + (r - per_S)] = s;
-      if (writes_m) n_area[size_t(z) * (dim + 1) + dim] = m;
+      float* dst = n_area + size_t(z) * (dim + 1);
+      dst[r - per_S] = s.x;
+      dst[r - per_S + 1] = s.y;
+      dst[r - per_S + 2] = s.z;
+      dst[r - per_S + 3] = s.w;
+      if (r == per_S) dst[dim] = m;
     }
   } else {
-    *mine = s;
+    mine[0] = s.x;
+    mine[1] = s.y;
+    mine[2] = s.z;
+    mine[3] = s.w;
   }
 }
 
@@ -415,9 +467,10 @@ PTB_API int ptb_mlstm_chunks_supports(int dim, int v_dim) {
 }
 PTB_API int ptb_mlstm_chunk_tokens() { return CH; }
 
-// float32 scratch of the chunked form: every chunk's S, n, (total, maximum) and the maximum before it
+// float32 scratch of the chunked form: every chunk's S, n, (total, maximum) and the maximum before it, and the
+// maximum after every sequence's last chunk (sequences are no more than chunks)
 PTB_API long long ptb_mlstm_chunks_scratch_floats(int n_chunks, int heads, int dim, int v_dim) {
-  return (long long)n_chunks * heads * ((long long)dim * v_dim + dim + 3);
+  return (long long)n_chunks * heads * ((long long)dim * v_dim + dim + 4);
 }
 
 // The three passes over a step's chunks. proj, gates, state, slots and out as ptb_mlstm_scan takes them (bfloat16
@@ -427,7 +480,7 @@ PTB_API int ptb_mlstm_chunks(const void* proj, int stride, const float* gates, f
                              const StepBatch* sb, const int* chunk_seq, const int* chunk_q0, const int* seq_chunk0, int n_chunks,
                              float* scratch, float* out, int heads, int dim, int v_dim, float q_scale, cudaStream_t stream) {
   if (sb->n_tokens <= 0 || n_chunks <= 0) return PTB_OK;
-  if (!ptb_mlstm_chunks_supports(dim, v_dim) || heads <= 0 || heads > 65535 || sb->n_seqs > 65535 ||
+  if (!ptb_mlstm_chunks_supports(dim, v_dim) || heads <= 0 || heads > 65535 || sb->n_seqs > 65535 || sb->n_seqs > n_chunks ||
       stride < 2 * heads * dim + heads * v_dim || state_stride < heads * (dim * v_dim + ((v_dim + VB - 1) / VB) * (dim + 1)))
     return PTB_ERR_SIZE;
   if (!aligned16(proj) || stride % 8 != 0 || !aligned16(scratch)) return PTB_ERR_ALIGN;
@@ -435,14 +488,19 @@ PTB_API int ptb_mlstm_chunks(const void* proj, int stride, const float* gates, f
   float* nsums = sums + size_t(n_chunks) * heads * dim * v_dim;
   float* meta = nsums + size_t(n_chunks) * heads * dim;
   float* m_before = meta + size_t(n_chunks) * heads * 2;
+  float* m_after = m_before + size_t(n_chunks) * heads;
   int rc;
 #define PTB_ML(DK, DV)                                                                                                          \
   do {                                                                                                                          \
     rc = launch_sum<DK, DV>(proj, stride, gates, *sb, chunk_seq, chunk_q0, n_chunks, sums, nsums, meta, heads, stream);         \
     if (rc != PTB_OK) return rc;                                                                                                \
-    const size_t per = size_t(heads) * (size_t(DK) * DV + DK);                                                                  \
-    mlstm_chunk_join_kernel<<<dim3(unsigned((per + 255) / 256), sb->n_seqs), 256, 0, stream>>>(                                 \
-        sums, nsums, meta, m_before, state, state_stride, slots, *sb, seq_chunk0, heads, DK, DV);                               \
+    mlstm_chunk_decay_kernel<<<dim3(unsigned((heads + 3) / 4), sb->n_seqs), 128, 0, stream>>>(                                  \
+        meta, m_before, m_after, state, state_stride, slots, *sb, seq_chunk0, heads, DK, DV);                                   \
+    rc = launch_status();                                                                                                       \
+    if (rc != PTB_OK) return rc;                                                                                                \
+    const size_t per = size_t(heads) * (size_t(DK) * DV + DK) / 4;                                                              \
+    mlstm_chunk_join_kernel<<<dim3(unsigned((per + 127) / 128), sb->n_seqs), 128, 0, stream>>>(                                 \
+        sums, nsums, meta, m_after, state, state_stride, slots, *sb, seq_chunk0, heads, DK, DV);                                \
     rc = launch_status();                                                                                                       \
     if (rc != PTB_OK) return rc;                                                                                                \
     return launch_out<DK, DV>(proj, stride, gates, *sb, chunk_seq, chunk_q0, n_chunks, sums, nsums, m_before, out, heads,       \

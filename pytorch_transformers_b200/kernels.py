@@ -101,7 +101,7 @@ def lib():
                      "ptb_linear_attention_chunks_mma", "ptb_linear_attention_token", "ptb_dyt", "ptb_mlstm_gates",
                      "ptb_mlstm_scan", "ptb_mlstm_max_dim", "ptb_mlstm_state_floats", "ptb_head_norm_gate",
                      "ptb_rope_norm_store", "ptb_talk_mix", "ptb_mlstm_chunks", "ptb_mlstm_chunks_supports",
-                     "ptb_mlstm_chunk_tokens"):
+                     "ptb_mlstm_chunk_tokens", "ptb_embed_rows"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -121,6 +121,16 @@ def gather_rows(ids: torch.Tensor, table: torch.Tensor, status: Optional[torch.T
     out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
     _check(lib().ptb_gather_rows(_dtype_code(table), _ptr(ids), _ptr(table), _ptr(out), ids.numel(),
                                  table.shape[1], table.shape[0], _ptr(status), _stream(table)), "gather_rows")
+    return out
+
+
+def embed_rows(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]) * scale (int32 ids; the product in float32): the first value of a float32
+    stream in one pass. An id out of range sets bit 0 of ``status``."""
+    _need_cuda(ids, table)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    _check(lib().ptb_embed_rows(_dtype_code(table), _ptr(ids), _ptr(table), _ptr(out), ids.numel(), table.shape[1],
+                                table.shape[0], ctypes.c_float(scale), _ptr(status), _stream(table)), "embed_rows")
     return out
 
 

@@ -45,6 +45,20 @@ def test_gather_rows(K, dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,scale", [(7, 1.0), (96, 3.0), (1000, 0.37), (4544, 1.7), (4546, 2.0)])
+def test_embed_rows(K, dtype, width, scale):
+    """Rows of a table widened to float32 and scaled there: what a gather, a widening and a product in float32 give."""
+    table = rnd(333, width, dtype=dtype)
+    ids = torch.tensor([0, 332, 5, 5, 17], dtype=torch.int32).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    out = K.embed_rows(ids, table, scale, status)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float() * scale)
+    assert status.item() == 0
+    K.embed_rows(torch.tensor([1, -1], dtype=torch.int32).cuda(), table, scale, status)
+    assert status.item() == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,width,eps", [(1, 64, 1e-5), (5, 96, 1e-6), (3, 4544, 1e-5), (2, 8192, 1e-5),
                                             (4, 1001, 1e-3), (2, 20000, 1e-5), (300, 4544, 1e-5), (2, 16384, 1e-5),
                                             (2, 16392, 1e-5), (7, 2056, 1e-5)])
