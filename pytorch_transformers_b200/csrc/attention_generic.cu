@@ -316,10 +316,8 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
                                        T* __restrict__ v_keep, int write_cache, int pairs) {
   extern __shared__ float rows[];   // per warp: a row of `dim` floats, then cos and sin of the rotated pairs
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int units = heads + 2 * kv_heads;
-  const long long u = (long long)blockIdx.x * (blockDim.x / 32) + warp;
-  if (u >= (long long)sb.n_tokens * units) return;
-  const int t = int(u / units), hh = int(u % units);
+  const int t = blockIdx.x, hh = blockIdx.y * (blockDim.x / 32) + warp;      // grid (tokens, groups of a block's warps)
+  if (hh >= heads + 2 * kv_heads) return;
   const T* row = proj + size_t(t) * stride;
   if (hh >= heads + kv_heads) {     // the values of one K/V head
     const int g = hh - heads - kv_heads;
@@ -471,22 +469,24 @@ int launch_attention(const void* q, const void* k_pool, const void* v_pool, void
 
 }  // namespace
 
-// cos and sin of position * inv_freq[i] for every token of the step: [n_tokens, pairs] each, float32.
+// cos and sin of position * inv_freq[i] for every token of the step, each times `factor` (a product in float32; 1 for a
+// plain rotation): [n_tokens, pairs] each, float32.
 __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq,
-                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int pairs) {
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int pairs,
+                                  float factor) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_tokens * pairs) return;
   float s, c;
   sincosf(float(tok_pos[i / pairs]) * inv_freq[i % pairs], &s, &c);
-  cos_out[i] = c;
-  sin_out[i] = s;
+  cos_out[i] = factor == 1.f ? c : c * factor;
+  sin_out[i] = factor == 1.f ? s : s * factor;
 }
 
 PTB_API int ptb_rope_table(const int* tok_pos, const float* inv_freq, float* cos_out, float* sin_out, int n_tokens,
-                           int pairs, cudaStream_t stream) {
+                           int pairs, float factor, cudaStream_t stream) {
   if (n_tokens <= 0 || pairs <= 0) return PTB_OK;
   const int total = n_tokens * pairs;
-  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(tok_pos, inv_freq, cos_out, sin_out, n_tokens, pairs);
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(tok_pos, inv_freq, cos_out, sin_out, n_tokens, pairs, factor);
   return launch_status();
 }
 
@@ -553,8 +553,9 @@ PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const f
   const int warps = 8, threads = 32 * warps;
   const size_t smem = size_t(warps) * (dim + 2 * size_t(rot_pairs)) * sizeof(float);
   if (smem > 48 * 1024) return PTB_ERR_SIZE;
-  const long long units = (long long)sb->n_tokens * (heads + 2 * kv_heads);
-  const unsigned blocks = unsigned((units + warps - 1) / warps);
+  const int units = heads + 2 * kv_heads;
+  if ((units + warps - 1) / warps > 65535) return PTB_ERR_SIZE;
+  const dim3 blocks(sb->n_tokens, (units + warps - 1) / warps);
   const size_t pair_bytes = dtype == PTB_F32 ? 8 : 4;
   const int pairs = (dim % 2 == 0 && stride % 2 == 0 && reinterpret_cast<uintptr_t>(proj) % pair_bytes == 0 &&
                      reinterpret_cast<uintptr_t>(q_out) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(k_pool) % pair_bytes == 0)

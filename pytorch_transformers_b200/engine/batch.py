@@ -282,12 +282,8 @@ class StepContext:
             return None
         key = getattr(position_part, "rotation_key", None) or id(position_part)
         if key not in self._rope:
-            cos, sin = K.rope_table(self.dev["tok_pos"], inv_freq)
             factor = float(getattr(position_part, "table_scale", 1.0))   # a factor on both tables (YaRN)
-            if factor != 1.0:
-                K.scale_(cos, factor)
-                K.scale_(sin, factor)
-            self._rope[key] = (cos, sin)
+            self._rope[key] = K.rope_table(self.dev["tok_pos"], inv_freq, factor)
         return self._rope[key]
 
     def plan(self, plan_key: str) -> StepPlan:

@@ -214,13 +214,14 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
     return y
 
 
-def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor):
-    """(cos, sin) of position * inv_freq for every token of a step: float32 [tokens, pairs] each."""
+def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor, factor: float = 1.0):
+    """(cos, sin) of position * inv_freq for every token of a step, each times ``factor`` (a float32 product):
+    float32 [tokens, pairs] each."""
     _need_cuda(tok_pos, inv_freq)
     n, pairs = tok_pos.numel(), inv_freq.numel()
     table = torch.empty((2, n, pairs), dtype=torch.float32, device=inv_freq.device)
     _check(lib().ptb_rope_table(_ptr(tok_pos), _ptr(inv_freq), _ptr(table[0]), _ptr(table[1]), n, pairs,
-                                _stream(inv_freq)), "rope_table")
+                                ctypes.c_float(factor), _stream(inv_freq)), "rope_table")
     return table[0], table[1]
 
 
