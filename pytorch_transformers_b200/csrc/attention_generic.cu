@@ -296,6 +296,28 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
+// four neighbouring entries in one access (the address a whole quad)
+__device__ __forceinline__ float4 load_quad(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load_quad(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store_quad(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store_quad(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&a);
+  u.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+// one half of rotate_pair: the entry `own` of a pair whose other entry is `other` (first: own c - other s; second:
+// own c + other s), with rotate_pair's roundings
+__device__ __forceinline__ float rotate_own(float own, float other, float c, float s, bool first) {
+  return first ? __fsub_rn(__fmul_rn(own, c), __fmul_rn(other, s)) : __fadd_rn(__fmul_rn(own, c), __fmul_rn(other, s));
+}
+
 // ------------------------------------------------------------------------------------------------
 // Separate projections q | k | v side by side in a row of `proj` (rows `stride` apart), an optional bias on all of
 // them (float32, added here in float32), then for every query and key head: rotation of the first 2 rot_pairs
@@ -313,7 +335,7 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
                                        const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int rot_pairs,
                                        int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm,
                                        const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ lam,
-                                       T* __restrict__ v_keep, int write_cache, int pairs) {
+                                       T* __restrict__ v_keep, int write_cache, int pairs, int quads) {
   extern __shared__ float rows[];   // per warp: a row of `dim` floats, then cos and sin of the rotated pairs
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x, hh = blockIdx.y * (blockDim.x / 32) + warp;      // grid (tokens, groups of a block's warps)
@@ -351,6 +373,40 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
     const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
     const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE];
     dst = k_pool + kv_offset(page, hh - heads, pos % PTB_PAGE, kv_heads, dim);
+  }
+  if (quads) {
+    // heads of up to 128 entries whose rotated part is a multiple of 8: four entries a lane in registers, the other
+    // entry of a rotated pair from the lane rot_pairs / 4 further (or back) by shuffle; no shared memory
+    const unsigned full = 0xffffffffu;
+    const int e = 4 * lane, P = rot_pairs / 4;
+    const bool on = e < dim;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 x = on ? load_quad(src + e) : zero;
+    if (bsrc && on) {
+      const float4 b = *reinterpret_cast<const float4*>(bsrc + e);
+      x = make_float4(x.x + b.x, x.y + b.y, x.z + b.z, x.w + b.w);
+    }
+    if (P > 0) {
+      const bool first = lane < P, rotated = lane < 2 * P;
+      const int other = first ? lane + P : (rotated ? lane - P : lane);
+      float4 c = zero, sn = zero;
+      if (rotated) {
+        c = *reinterpret_cast<const float4*>(rope_cos + size_t(t) * rot_pairs + 4 * (first ? lane : lane - P));
+        sn = *reinterpret_cast<const float4*>(rope_sin + size_t(t) * rot_pairs + 4 * (first ? lane : lane - P));
+      }
+      const float4 y = make_float4(__shfl_sync(full, x.x, other), __shfl_sync(full, x.y, other), __shfl_sync(full, x.z, other),
+                                   __shfl_sync(full, x.w, other));
+      if (rotated)
+        x = make_float4(rotate_own(x.x, y.x, c.x, sn.x, first), rotate_own(x.y, y.y, c.y, sn.y, first),
+                        rotate_own(x.z, y.z, c.z, sn.z, first), rotate_own(x.w, y.w, c.w, sn.w, first));
+    }
+    float rstd = 1.f;
+    if (unit_norm) {
+      const float ss = fmaf(x.w, x.w, fmaf(x.z, x.z, fmaf(x.y, x.y, x.x * x.x)));
+      rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+    }
+    if (on) store_quad(dst + e, make_float4(x.x * rstd, x.y * rstd, x.z * rstd, x.w * rstd));
+    return;
   }
   for (int i = lane; i < rot_pairs; i += 32) {       // issued with the row's loads
     cs[i] = rope_cos[size_t(t) * rot_pairs + i];
@@ -560,16 +616,22 @@ PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const f
   const int pairs = (dim % 2 == 0 && stride % 2 == 0 && reinterpret_cast<uintptr_t>(proj) % pair_bytes == 0 &&
                      reinterpret_cast<uintptr_t>(q_out) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(k_pool) % pair_bytes == 0)
                         ? 1 : 0;
+  const size_t quad_bytes = 2 * pair_bytes;
+  const int quads = (dim % 4 == 0 && dim <= 128 && rot_pairs % 4 == 0 && stride % 4 == 0 &&
+                     reinterpret_cast<uintptr_t>(proj) % quad_bytes == 0 && reinterpret_cast<uintptr_t>(q_out) % quad_bytes == 0 &&
+                     reinterpret_cast<uintptr_t>(k_pool) % quad_bytes == 0 && (bias == nullptr || aligned16(bias)) &&
+                     (rot_pairs == 0 || (aligned16(rope_cos) && aligned16(rope_sin))))
+                        ? 1 : 0;
   if (dtype == PTB_F32)
     rope_norm_store_kernel<float><<<blocks, threads, smem, stream>>>(
         (const float*)proj, stride, bias, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, rope_cos, rope_sin, rot_pairs,
         heads, kv_heads, dim, v_dim, eps, unit_norm, (const float*)v_first, v_first_stride, lam, (float*)v_keep, write_cache,
-        pairs);
+        pairs, quads);
   else if (dtype == PTB_BF16)
     rope_norm_store_kernel<__nv_bfloat16><<<blocks, threads, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, bias, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
         rope_cos, rope_sin, rot_pairs, heads, kv_heads, dim, v_dim, eps, unit_norm, (const __nv_bfloat16*)v_first,
-        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache, pairs);
+        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache, pairs, quads);
   else
     return PTB_ERR_DTYPE;
   return launch_status();
