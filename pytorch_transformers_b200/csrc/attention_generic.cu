@@ -137,8 +137,9 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
 // Values may have a size of their own (v_dim; the V pool is [pages][kv_heads][PTB_PAGE][v_dim]).
 // With `sinks` [heads] every row's softmax denominator holds one more term, exp(sink_h), taken as stored
 // (`scale` is not applied to it); no key or value is read for it. With `gate` (row t, head h at gate[t * gate_stride + h]) the head's
-// output is multiplied by sigmoid(gate); `out_scale` multiplies everything. Output row t, head h starts
-// at out[t * out_stride + h * v_dim].
+// output is multiplied by sigmoid(gate); with `gate_wide` the gate has a number per output entry instead (row t, head h,
+// entry e at gate[t * gate_stride + h * v_dim + e]); `out_scale` multiplies everything. Output row t, head h starts
+// at out[t * out_stride + h * v_dim]. `softcap` > 0: score <- softcap * tanh(score / softcap) after the scale.
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
@@ -146,7 +147,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          const int* __restrict__ tile_q0, const float* __restrict__ alibi_slopes, int heads,
                          int kv_heads, int head_dim, float scale, int window, int v_dim,
                          const float* __restrict__ sinks, const T* __restrict__ gate, int gate_stride, float out_scale,
-                         int out_stride, int keep_first, float* __restrict__ out_wide) {
+                         int out_stride, int keep_first, float* __restrict__ out_wide, float softcap, int gate_wide) {
   extern __shared__ float smem[];
   const int wide = max(head_dim, v_dim);
   float* qs = smem;                                 // [BQ][head_dim]
@@ -214,6 +215,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
       if (visible) {
         if (alibi_slopes) dot += alibi_bias(slope, key_pos);
         sc = dot * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
       }
       s[jj] = sc;
       m_blk = fmaxf(m_blk, sc);
@@ -266,7 +268,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
       l_run = l_run * keep + expf(sink - m_all);
     }
     float inv = (l_run > 0.f ? 1.f / l_run : 0.f) * keep * out_scale;
-    if (gate) inv *= 1.f / (1.f + expf(-to_f(gate[size_t(start + q0 + r) * gate_stride + h])));
+    if (gate && !gate_wide) inv *= 1.f / (1.f + expf(-to_f(gate[size_t(start + q0 + r) * gate_stride + h])));
     if (out_wide) {
       // float32 [token][head][K/V head][v_dim]
       float* o = out_wide + ((size_t(start + q0 + r) * heads + h) * kv_heads + gv) * v_dim;
@@ -278,10 +280,11 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
       return;
     }
     T* o = out + size_t(start + q0 + r) * out_stride + size_t(h) * v_dim;
+    const T* ge = (gate && gate_wide) ? gate + size_t(start + q0 + r) * gate_stride + size_t(h) * v_dim : nullptr;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
       const int e = c + 8 * i;
-      if (e < v_dim) o[e] = from_f<T>(acc[i] * inv);
+      if (e < v_dim) o[e] = from_f<T>(acc[i] * inv * (ge ? 1.f / (1.f + expf(-to_f(ge[e]))) : 1.f));
     }
   }
 }
@@ -326,7 +329,9 @@ __device__ __forceinline__ float rotate_own(float own, float other, float c, flo
 // root, no gain). Values: v <- (1 - lam) v + lam v_first with the values of the same token that an earlier layer
 // kept (`v_first`, rows v_first_stride apart; lam one float32 on the device); `v_keep` receives this layer's own
 // values (with bias, before any mixing) for later layers. Keys and values go into the paged pools at the tokens'
-// positions, queries to q_out [tokens, heads, dim]. A warp per (token, head): query heads, then key heads, then the
+// positions, queries to q_out [tokens, heads, dim]. With `norm_first` the norm comes before the rotation and takes
+// gains (`q_gain`, `k_gain` [dim] float32, null: none). With temp_every > 0 a query at position p is multiplied by
+// 1 + temp_coef ln(floor((p + 1) / temp_every) + 1) at the end, in float32. A warp per (token, head): query heads, then key heads, then the
 // K/V heads' values; the warps of a block share nothing, so a head's chain of loads, rotation, sum and stores waits
 // for no other.
 template <typename T>
@@ -335,7 +340,9 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
                                        const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int rot_pairs,
                                        int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm,
                                        const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ lam,
-                                       T* __restrict__ v_keep, int write_cache, int pairs, int quads) {
+                                       T* __restrict__ v_keep, int write_cache, int pairs, int quads,
+                                       const float* __restrict__ q_gain, const float* __restrict__ k_gain, int norm_first,
+                                       float temp_coef, int temp_every) {
   extern __shared__ float rows[];   // per warp: a row of `dim` floats, then cos and sin of the rotated pairs
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x, hh = blockIdx.y * (blockDim.x / 32) + warp;      // grid (tokens, groups of a block's warps)
@@ -367,8 +374,11 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
   const T* src = row + size_t(hh) * dim;
   const float* bsrc = bias ? bias + size_t(hh) * dim : nullptr;
   T* dst;
+  const float* gain = is_q ? q_gain : k_gain;     // null: the norm has no gains
+  float last = 1.f;     // what the finished row is multiplied by: the query temperature of the token's position
   if (is_q) {
     dst = q_out + (size_t(t) * heads + hh) * dim;
+    if (temp_every > 0) last = 1.f + temp_coef * logf(float((sb.tok_pos[t] + 1) / temp_every) + 1.f);
   } else {
     const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
     const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE];
@@ -386,6 +396,12 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
       const float4 b = *reinterpret_cast<const float4*>(bsrc + e);
       x = make_float4(x.x + b.x, x.y + b.y, x.z + b.z, x.w + b.w);
     }
+    if (unit_norm && norm_first) {      // the norm (with its gains) comes before the rotation
+      const float ss = fmaf(x.w, x.w, fmaf(x.z, x.z, fmaf(x.y, x.y, x.x * x.x)));
+      const float r = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+      const float4 g = (gain && on) ? *reinterpret_cast<const float4*>(gain + e) : make_float4(1.f, 1.f, 1.f, 1.f);
+      x = make_float4(x.x * r * g.x, x.y * r * g.y, x.z * r * g.z, x.w * r * g.w);
+    }
     if (P > 0) {
       const bool first = lane < P, rotated = lane < 2 * P;
       const int other = first ? lane + P : (rotated ? lane - P : lane);
@@ -400,10 +416,10 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
         x = make_float4(rotate_own(x.x, y.x, c.x, sn.x, first), rotate_own(x.y, y.y, c.y, sn.y, first),
                         rotate_own(x.z, y.z, c.z, sn.z, first), rotate_own(x.w, y.w, c.w, sn.w, first));
     }
-    float rstd = 1.f;
-    if (unit_norm) {
+    float rstd = last;
+    if (unit_norm && !norm_first) {
       const float ss = fmaf(x.w, x.w, fmaf(x.z, x.z, fmaf(x.y, x.y, x.x * x.x)));
-      rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+      rstd = last / sqrtf(warp_sum(ss) / float(dim) + eps);
     }
     if (on) store_quad(dst + e, make_float4(x.x * rstd, x.y * rstd, x.z * rstd, x.w * rstd));
     return;
@@ -422,6 +438,13 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
     for (int e = lane; e < dim; e += 32) buf[e] = to_f(src[e]) + (bsrc ? bsrc[e] : 0.f);
   }
   __syncwarp();
+  if (unit_norm && norm_first) {
+    float ss = 0.f;
+    for (int e = lane; e < dim; e += 32) ss = fmaf(buf[e], buf[e], ss);
+    const float r = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+    for (int e = lane; e < dim; e += 32) buf[e] = buf[e] * r * (gain ? gain[e] : 1.f);
+    __syncwarp();
+  }
   for (int i = lane; i < rot_pairs; i += 32) {
     float a, b;
     rotate_pair(buf[i], buf[i + rot_pairs], cs[i], cs[rot_pairs + i], a, b);
@@ -429,11 +452,11 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ proj, int stride, c
     buf[i + rot_pairs] = b;
   }
   __syncwarp();
-  float rstd = 1.f;
-  if (unit_norm) {
+  float rstd = last;
+  if (unit_norm && !norm_first) {
     float ss = 0.f;
     for (int e = lane; e < dim; e += 32) ss = fmaf(buf[e], buf[e], ss);
-    rstd = 1.0f / sqrtf(warp_sum(ss) / float(dim) + eps);
+    rstd = last / sqrtf(warp_sum(ss) / float(dim) + eps);
   }
   if (pairs) {
     for (int e = 2 * lane; e < dim; e += 64) store_pair(dst + e, buf[e] * rstd, buf[e + 1] * rstd);
@@ -505,7 +528,8 @@ template <typename T>
 int launch_attention(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch& sb,
                      const int* tile_seq, const int* tile_q0, int n_tiles, const float* slopes, int heads,
                      int kv_heads, int head_dim, float scale, int window, int v_dim, const float* sinks, const void* gate,
-                     int gate_stride, float out_scale, int out_stride, int keep_first, float* out_wide, cudaStream_t stream) {
+                     int gate_stride, float out_scale, int out_stride, int keep_first, float* out_wide, float softcap,
+                     int gate_wide, cudaStream_t stream) {
   const int wide = head_dim > v_dim ? head_dim : v_dim;
   const size_t smem = sizeof(float) * (size_t(BQ) * head_dim + size_t(PTB_PAGE) * (wide + 1) + BQ * PTB_PAGE);
   static size_t configured = 48 * 1024;  // per element type: raised when a larger head size first comes
@@ -519,7 +543,8 @@ int launch_attention(const void* q, const void* k_pool, const void* v_pool, void
   attention_generic_kernel<T><<<grid, THREADS, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool,
                                                                (T*)out, sb, tile_seq, tile_q0, slopes, heads, kv_heads,
                                                                head_dim, scale, window, v_dim, sinks, (const T*)gate,
-                                                               gate_stride, out_scale, out_stride, keep_first, out_wide);
+                                                               gate_stride, out_scale, out_stride, keep_first, out_wide,
+                                                               softcap, gate_wide);
   return launch_status();
 }
 
@@ -569,27 +594,40 @@ PTB_API int ptb_split_rotate_store(int dtype, const void* fused, void* q_out, vo
   return launch_status();
 }
 
-PTB_API int ptb_attention_generic(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
+PTB_API int ptb_attention_generic_capped(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
                                   const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
                                   const float* alibi_slopes, int heads, int kv_heads, int head_dim, float scale,
                                   int window, int v_dim, const float* sinks, const void* gate, int gate_stride,
-                                  float out_scale, int out_stride, int keep_first, float* out_wide, cudaStream_t stream) {
+                                  float out_scale, int out_stride, int keep_first, float* out_wide, float softcap, int gate_wide,
+                                         cudaStream_t stream) {
+  // softcap > 0: scores are soft-capped; gate_wide: the gate has heads * v_dim numbers a token (gate_stride at least that)
   // keep_first: with a window, the sequence's first keep_first positions stay visible too. out_wide (float32
   // [tokens][heads][kv_heads][v_dim], or null): every head's weights on every K/V head's values instead of `out`.
   if (n_tiles <= 0) return PTB_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim <= 0 || head_dim > MAX_D || heads > 65535 ||
       v_dim <= 0 || v_dim > MAX_D || (out_wide == nullptr && out_stride < heads * v_dim) || keep_first < 0 ||
-      (out_wide != nullptr && kv_heads > 65535))
+      (out_wide != nullptr && kv_heads > 65535) || softcap < 0.f ||
+      (gate != nullptr && gate_stride < (gate_wide ? heads * v_dim : heads)))
     return PTB_ERR_SIZE;
   if (dtype == PTB_F32)
     return launch_attention<float>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
                                    kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride, out_scale, out_stride,
-                                   keep_first, out_wide, stream);
+                                   keep_first, out_wide, softcap, gate_wide, stream);
   if (dtype == PTB_BF16)
     return launch_attention<__nv_bfloat16>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, alibi_slopes,
                                            heads, kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride,
-                                           out_scale, out_stride, keep_first, out_wide, stream);
+                                           out_scale, out_stride, keep_first, out_wide, softcap, gate_wide, stream);
   return PTB_ERR_DTYPE;
+}
+
+PTB_API int ptb_attention_generic(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
+                                  const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                  const float* alibi_slopes, int heads, int kv_heads, int head_dim, float scale,
+                                  int window, int v_dim, const float* sinks, const void* gate, int gate_stride,
+                                  float out_scale, int out_stride, int keep_first, float* out_wide, cudaStream_t stream) {
+  return ptb_attention_generic_capped(dtype, q, k_pool, v_pool, out, sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
+                                      kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride, out_scale, out_stride,
+                                      keep_first, out_wide, 0.f, 0, stream);
 }
 
 // rows of a tile of the general kernel, for the host that builds the tile lists
@@ -597,14 +635,16 @@ PTB_API int ptb_attention_generic_tile_rows() { return BQ; }
 
 // bias: float32 [(heads + kv_heads) dim + kv_heads v_dim] or null; rope_cos / rope_sin: float32 [tokens, rot_pairs] or null;
 // v_first (rows v_first_stride apart), lam, v_keep [tokens, kv_heads v_dim]: null where not used.
-PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const float* bias, void* q_out, void* k_pool,
+PTB_API int ptb_qk_prepare_store(int dtype, const void* proj, int stride, const float* bias, void* q_out, void* k_pool,
                                 void* v_pool, const StepBatch* sb, const float* rope_cos, const float* rope_sin, int rot_pairs,
                                 int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm, const void* v_first,
-                                int v_first_stride, const float* lam, void* v_keep, int write_cache, cudaStream_t stream) {
+                                int v_first_stride, const float* lam, void* v_keep, int write_cache, const float* q_gain,
+                                 const float* k_gain, int norm_first, float temp_coef, int temp_every, cudaStream_t stream) {
   if (sb->n_tokens <= 0) return PTB_OK;
   if (heads <= 0 || kv_heads <= 0 || dim <= 0 || v_dim <= 0 || stride < (heads + kv_heads) * dim + kv_heads * v_dim ||
       rot_pairs < 0 || 2 * rot_pairs > dim || (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) ||
-      (v_first != nullptr && lam == nullptr) || dim > 4096)
+      (v_first != nullptr && lam == nullptr) || dim > 4096 || temp_every < 0 ||
+      ((q_gain != nullptr || k_gain != nullptr) && !(unit_norm && norm_first)))
     return PTB_ERR_SIZE;
   const int warps = 8, threads = 32 * warps;
   const size_t smem = size_t(warps) * (dim + 2 * size_t(rot_pairs)) * sizeof(float);
@@ -619,22 +659,33 @@ PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const f
   const size_t quad_bytes = 2 * pair_bytes;
   const int quads = (dim % 4 == 0 && dim <= 128 && rot_pairs % 4 == 0 && stride % 4 == 0 &&
                      reinterpret_cast<uintptr_t>(proj) % quad_bytes == 0 && reinterpret_cast<uintptr_t>(q_out) % quad_bytes == 0 &&
-                     reinterpret_cast<uintptr_t>(k_pool) % quad_bytes == 0 && (bias == nullptr || aligned16(bias)) &&
+                     reinterpret_cast<uintptr_t>(k_pool) % quad_bytes == 0 && (bias == nullptr || aligned16(bias)) && (q_gain == nullptr || aligned16(q_gain)) &&
+                     (k_gain == nullptr || aligned16(k_gain)) &&
                      (rot_pairs == 0 || (aligned16(rope_cos) && aligned16(rope_sin))))
                         ? 1 : 0;
   if (dtype == PTB_F32)
     rope_norm_store_kernel<float><<<blocks, threads, smem, stream>>>(
         (const float*)proj, stride, bias, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, rope_cos, rope_sin, rot_pairs,
         heads, kv_heads, dim, v_dim, eps, unit_norm, (const float*)v_first, v_first_stride, lam, (float*)v_keep, write_cache,
-        pairs, quads);
+        pairs, quads, q_gain, k_gain, norm_first, temp_coef, temp_every);
   else if (dtype == PTB_BF16)
     rope_norm_store_kernel<__nv_bfloat16><<<blocks, threads, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, bias, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
         rope_cos, rope_sin, rot_pairs, heads, kv_heads, dim, v_dim, eps, unit_norm, (const __nv_bfloat16*)v_first,
-        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache, pairs, quads);
+        v_first_stride, lam, (__nv_bfloat16*)v_keep, write_cache, pairs, quads, q_gain, k_gain, norm_first, temp_coef,
+        temp_every);
   else
     return PTB_ERR_DTYPE;
   return launch_status();
+}
+
+PTB_API int ptb_rope_norm_store(int dtype, const void* proj, int stride, const float* bias, void* q_out, void* k_pool,
+                                void* v_pool, const StepBatch* sb, const float* rope_cos, const float* rope_sin, int rot_pairs,
+                                int heads, int kv_heads, int dim, int v_dim, float eps, int unit_norm, const void* v_first,
+                                int v_first_stride, const float* lam, void* v_keep, int write_cache, cudaStream_t stream) {
+  return ptb_qk_prepare_store(dtype, proj, stride, bias, q_out, k_pool, v_pool, sb, rope_cos, rope_sin, rot_pairs, heads,
+                              kv_heads, dim, v_dim, eps, unit_norm, v_first, v_first_stride, lam, v_keep, write_cache, nullptr,
+                              nullptr, 0, 0.f, 0, stream);
 }
 
 PTB_API int ptb_talk_mix(int dtype, const float* wide, const float* talk, void* out, int out_stride, int n_tokens, int heads,

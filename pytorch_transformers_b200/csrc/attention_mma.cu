@@ -33,7 +33,22 @@ struct MmaParams {
   // not null: every head's weights on every K/V head's values, float32 [tokens][heads][kv_heads][D]; blockIdx.y then
   // also walks the K/V head whose values a block reads, and `out`, sinks, gate and factor are not used
   float* out_wide;
+  // > 0: score <- softcap * tanh(score / softcap) after the scale
+  float softcap;
+  // the gate has a number per output entry (row t, head h, entry e at gate[t * gate_stride + h * D + e]) instead of one per head
+  int gate_wide;
 };
+
+// A raw product q . k as a score in log2 units: scaled, and soft-capped where the design says so. tanh(x) is formed as
+// 1 - 2 / (exp(2 x) + 1): an absolute error of a few 1e-7, which the cap multiplies.
+__device__ __forceinline__ float score_log2(const MmaParams& p, float raw, float sl2) {
+  if (p.softcap > 0.f) {
+    const float t = fast_exp2(raw * p.scale * (2.f * 1.4426950408889634f / p.softcap));
+    return (p.softcap * 1.4426950408889634f) * (1.f - __fdividef(2.f, t + 1.f));
+  }
+  return raw * sl2;
+}
+__device__ __forceinline__ float sigmoid_bf16(__nv_bfloat16 v) { return 1.f / (1.f + expf(-__bfloat162float(v))); }
 
 // What a row's accumulated O is multiplied by at the end: 1 / (sum of the keys' weights + the sink's weight), the
 // gate and the factor. m, l: the row's running maximum (log2 units) and sum.
@@ -45,7 +60,7 @@ __device__ __forceinline__ float finish_row(const MmaParams& p, float m, float l
     l = l * keep + exp2f(s2 - m_all);
   }
   float f = (l > 0.f ? 1.f / l : 0.f) * keep * p.out_scale;
-  if (p.gate) f *= 1.f / (1.f + expf(-__bfloat162float(p.gate[size_t(token) * p.gate_stride + head])));
+  if (p.gate && !p.gate_wide) f *= 1.f / (1.f + expf(-__bfloat162float(p.gate[size_t(token) * p.gate_stride + head])));
   return f;
 }
 
@@ -187,7 +202,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         for (int j = 0; j < KEYS / 8; ++j) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float v = s[j][e] * sl2;
+            const float v = score_log2(p, s[j][e], sl2);
             s[j][e] = v;
             m_blk[e >> 1] = fmaxf(m_blk[e >> 1], v);
           }
@@ -203,7 +218,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             if (p.window > 0) visible = visible && (key_pos > row_pos[i] - p.window || key_pos < p.keep_first);
             float v = s[j][e];
             if (alibi_slopes) v += alibi_bias(slope[i], key_pos);
-            v = visible ? v * sl2 : -INFINITY;
+            v = visible ? score_log2(p, v, sl2) : -INFINITY;
             s[j][e] = v;
             m_blk[i] = fmaxf(m_blk[i], v);
           }
@@ -285,6 +300,16 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       }
       const float inv = finish_row(p, m_run[i], l_run[i], token, head);
       __nv_bfloat16* dst = out + size_t(token) * p.out_stride + size_t(head) * D + t4 * 2;
+      if (p.gate && p.gate_wide) {
+        const __nv_bfloat16* ge = p.gate + size_t(token) * p.gate_stride + size_t(head) * D + t4 * 2;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+          const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(ge + j * 8);
+          *reinterpret_cast<uint32_t*>(dst + j * 8) =
+              pack_bf16(o[j][2 * i] * inv * sigmoid_bf16(g2.x), o[j][2 * i + 1] * inv * sigmoid_bf16(g2.y));
+        }
+        continue;
+      }
 #pragma unroll
       for (int j = 0; j < D / 8; ++j)
         *reinterpret_cast<uint32_t*>(dst + j * 8) = pack_bf16(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
@@ -357,8 +382,9 @@ attention_mma_reduce_kernel(const float* __restrict__ part_o, const float* __res
   }
   const float inv = finish_row(p, m, l, token, head);
   __nv_bfloat16* dst = out + size_t(token) * p.out_stride + size_t(head) * D + lane * PER;
+  const __nv_bfloat16* ge = (p.gate && p.gate_wide) ? p.gate + size_t(token) * p.gate_stride + size_t(head) * D + lane * PER : nullptr;
 #pragma unroll
-  for (int e = 0; e < PER; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
+  for (int e = 0; e < PER; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv * (ge ? sigmoid_bf16(ge[e]) : 1.f));
 }
 
 template <int D>
@@ -420,15 +446,18 @@ PTB_API long long ptb_attention_mma_scratch_floats(int n_tiles, int heads, int k
 // keep_first: with a window, the sequence's first keep_first positions stay visible too. out_wide (float32
 // [tokens, heads, kv_heads, head_dim]; then out, sinks and gate are null and out_scale 1): every head's softmax
 // weights applied to every K/V head's values; the scratch of a launch with splits is kv_heads times as large.
-PTB_API int ptb_attention_mma_kept(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+PTB_API int ptb_attention_mma_capped(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                               const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
                               const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
                               int tokens_per_tile, int n_splits, int warps, float scale, int window,
                               const float* sinks, const void* gate, int gate_stride, float out_scale, int out_stride,
-                              int wide_weights, int keep_first, float* out_wide, cudaStream_t stream) {
+                              int wide_weights, int keep_first, float* out_wide, float softcap, int gate_wide,
+                              cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
   if (out_stride == 0) out_stride = heads * head_dim;
-  if (out_stride < heads * head_dim || out_stride % 2 != 0 || (gate != nullptr && gate_stride < heads)) return PTB_ERR_SIZE;
+  if (out_stride < heads * head_dim || out_stride % 2 != 0 || (gate != nullptr && gate_stride < (gate_wide ? heads * head_dim : heads)) ||
+      softcap < 0.f || (gate != nullptr && gate_wide && (gate_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(gate) & 3) != 0)))
+    return PTB_ERR_SIZE;
   if (keep_first < 0 || (out_wide != nullptr && (out != nullptr || sinks != nullptr || gate != nullptr || out_scale != 1.f)))
     return PTB_ERR_SIZE;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || warps < 1 || warps > 8 || hpk < 1 ||
@@ -445,6 +474,7 @@ PTB_API int ptb_attention_mma_kept(const void* q, const void* k_pool, const void
   p.sinks = sinks; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride; p.out_scale = out_scale;
   p.out_stride = out_stride; p.wide_weights = wide_weights;
   p.keep_first = window > 0 ? keep_first : 0; p.out_wide = out_wide;
+  p.softcap = softcap; p.gate_wide = gate_wide;
   const long long o_floats = (long long)n_tiles * y_blocks * n_splits * (warps * 16) * head_dim;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + o_floats : nullptr;
@@ -458,6 +488,18 @@ PTB_API int ptb_attention_mma_kept(const void* q, const void* k_pool, const void
     default:
       return PTB_ERR_SIZE;
   }
+}
+
+// softcap 0 and a gate per head: the form before the soft cap and the gate per entry were added
+PTB_API int ptb_attention_mma_kept(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+                              const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                              const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
+                              int tokens_per_tile, int n_splits, int warps, float scale, int window,
+                              const float* sinks, const void* gate, int gate_stride, float out_scale, int out_stride,
+                              int wide_weights, int keep_first, float* out_wide, cudaStream_t stream) {
+  return ptb_attention_mma_capped(q, k_pool, v_pool, out, scratch, sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
+                                  kv_heads, head_dim, hpk, tokens_per_tile, n_splits, warps, scale, window, sinks, gate,
+                                  gate_stride, out_scale, out_stride, wide_weights, keep_first, out_wide, 0.f, 0, stream);
 }
 
 PTB_API int ptb_attention_mma_gated(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,

@@ -22,7 +22,7 @@ enum {
 
 // Activations, by the codes that every entry point with an `act` argument takes. This is the one table:
 // a new activation is an entry here, a case in apply_activation and a name in kernels.ACTIVATIONS.
-enum { PTB_ACT_NONE = 0, PTB_ACT_GELU_ERF = 1, PTB_ACT_GELU_TANH = 2, PTB_ACT_RELU = 3, PTB_ACT_RELU_SQUARED = 4, PTB_ACT_COUNT = 5 };
+enum { PTB_ACT_NONE = 0, PTB_ACT_GELU_ERF = 1, PTB_ACT_GELU_TANH = 2, PTB_ACT_RELU = 3, PTB_ACT_RELU_SQUARED = 4, PTB_ACT_SILU = 5, PTB_ACT_COUNT = 6 };
 inline bool activation_known(int act) { return act >= 0 && act < PTB_ACT_COUNT; }
 __device__ __forceinline__ float apply_activation(float v, int act) {
   switch (act) {
@@ -30,6 +30,7 @@ __device__ __forceinline__ float apply_activation(float v, int act) {
     case PTB_ACT_GELU_TANH: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
     case PTB_ACT_RELU: return fmaxf(v, 0.f);
     case PTB_ACT_RELU_SQUARED: { const float r = fmaxf(v, 0.f); return r * r; }
+    case PTB_ACT_SILU: return v / (1.0f + expf(-v));
     default: return v;
   }
 }

@@ -629,3 +629,48 @@ PTB_API int ptb_glu_clamp(int dtype, const void* in, void* out, int rows, int f,
     return PTB_ERR_DTYPE;
   return launch_status();
 }
+
+// A gated unit between a feed-forward's two products: in [rows, 2 F] holds the gate's columns, then the up branch's;
+// out = act(gate) * up [rows, F], float32 arithmetic, rounded once.
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int f, int act) {
+  const size_t total = size_t(rows) * f, stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / f, c = i % f;
+    out[i] = from_f<T>(apply_activation(to_f(in[r * 2 * f + c]), act) * to_f(in[r * 2 * f + f + c]));
+  }
+}
+
+// the same for bfloat16 rows of whole 16-byte words: eight values a thread
+__global__ void glu_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int rows, int f,
+                                      int act) {
+  const int f8 = f / 8;
+  const size_t total = size_t(rows) * f8, stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / f8, c = (i % f8) * 8;
+    float g[8], u[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(in + r * 2 * f + c), g);
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(in + r * 2 * f + f + c), u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = apply_activation(g[e], act) * u[e];
+    *reinterpret_cast<uint4*>(out + r * f + c) = pack_bf16x8(g);
+  }
+}
+
+PTB_API int ptb_glu_act(int dtype, const void* in, void* out, int rows, int f, int act, cudaStream_t stream) {
+  if (rows <= 0) return PTB_OK;
+  if (f <= 0 || !activation_known(act)) return PTB_ERR_SIZE;
+  if (dtype == PTB_BF16 && f % 8 == 0 && aligned16(in) && aligned16(out)) {
+    glu_act_bf16x8_kernel<<<grid_for(size_t(rows) * (f / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)in,
+                                                                                      (__nv_bfloat16*)out, rows, f, act);
+    return launch_status();
+  }
+  const int blocks = grid_for(size_t(rows) * f, 256);
+  if (dtype == PTB_F32)
+    glu_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, rows, f, act);
+  else if (dtype == PTB_BF16)
+    glu_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, f, act);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}

@@ -50,12 +50,12 @@ route_logits_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ correction, int* __restrict__ ids,
                     float* __restrict__ gates, int n_tokens, int n, int n_groups, int keep, int top,
-                    float route_scale, int score_kind) {
+                    float route_scale, int score_kind, int z_stride, int group_top, int normalize) {
   extern __shared__ float sm[];   // per warp: n choice scores, n_groups group scores
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= n_tokens) return;
-  const float* zs = zs_all + size_t(t) * n;
+  const float* zs = zs_all + size_t(t) * z_stride;
   float* choice = sm + size_t(warp) * (n + n_groups);
   float* gscore = choice + n;
   float z[ROUTE_VPL], s[ROUTE_VPL];
@@ -85,9 +85,17 @@ route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ 
   __syncwarp();
   const int per = n / n_groups;
   for (int g = lane; g < n_groups; g += 32) {
-    float m = -INFINITY;
-    for (int i = 0; i < per; ++i) m = fmaxf(m, choice[g * per + i]);
-    gscore[g] = m;
+    float m = -INFINITY, m2 = -INFINITY;      // the group's largest and second largest choice scores
+    for (int i = 0; i < per; ++i) {
+      const float c = choice[g * per + i];
+      if (c > m) {
+        m2 = m;
+        m = c;
+      } else {
+        m2 = fmaxf(m2, c);
+      }
+    }
+    gscore[g] = (group_top == 2 && per > 1) ? m + m2 : m;
   }
   __syncwarp();
   if (keep < n_groups) {
@@ -109,6 +117,7 @@ route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ 
     cs[v] = (e < n) ? choice[e] : -INFINITY;
     open[v] = e < n;
   }
+  float chosen_sum = 0.f;     // of the chosen outputs' scores, in the order of the choice (every lane holds it)
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -129,9 +138,9 @@ route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ 
         best_e = oe;
       }
     }
+    float sv = 0.f;
     if (best_e % 32 == lane) {
       const int v = best_e / 32;
-      float sv = 0.f;
 #pragma unroll
       for (int u = 0; u < ROUTE_VPL; ++u)
         if (u == v) {
@@ -139,8 +148,18 @@ route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ 
           open[u] = false;
         }
       ids[size_t(t) * top + k] = best_e;
-      gates[size_t(t) * top + k] = sv * route_scale;
+      if (!normalize) gates[size_t(t) * top + k] = sv * route_scale;
     }
+    if (normalize) {
+      sv = __shfl_sync(0xffffffffu, sv, best_e % 32);
+      chosen_sum += sv;
+      if (lane == 0) gates[size_t(t) * top + k] = sv;
+    }
+  }
+  if (normalize && lane == 0) {
+    // weights = scores / (their sum + 1e-20) * scale
+    const float total = chosen_sum + 1e-20f;
+    for (int k = 0; k < top; ++k) gates[size_t(t) * top + k] = gates[size_t(t) * top + k] / total * route_scale;
   }
 }
 
@@ -291,14 +310,18 @@ expert_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, TO* __res
 
 // out[t] = base[t] + sum_k gate[t, k] * (expert output row of the pair, or h[t] for an identity expert),
 // summed in float32 in the order of the choice (gate null: every weight is one); base and out are float32 or of
-// the model dtype (TB).
+// the model dtype (TB). With `shared` (float32 [tokens, width]) the result also holds sigmoid(shared_gate[t]) * shared[t]
+// (shared_gate null: the rows as they are).
 // One block per token.
 template <typename T, typename TB>
 __global__ void expert_combine_kernel(const TB* __restrict__ base, const T* __restrict__ h,
                                       const float* __restrict__ y, const int* __restrict__ ids,
                                       const float* __restrict__ gates, const int* __restrict__ row_of_pair,
-                                      TB* __restrict__ out, int width, int top) {
+                                      TB* __restrict__ out, int width, int top, const float* __restrict__ shared,
+                                      const float* __restrict__ shared_gate, int shared_gate_stride) {
   const int t = blockIdx.x;
+  // an expert that every token uses: its float32 rows times sigmoid(one logit per token), added last
+  const float sg = shared ? (shared_gate ? 1.f / (1.f + expf(-shared_gate[size_t(t) * shared_gate_stride])) : 1.f) : 0.f;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -306,6 +329,7 @@ __global__ void expert_combine_kernel(const TB* __restrict__ base, const T* __re
       const float v = (row >= 0) ? y[size_t(row) * width + i] : to_f(h[size_t(t) * width + i]);
       s = fmaf(gates ? gates[size_t(t) * top + k] : 1.f, v, s);
     }
+    if (shared) s = fmaf(sg, shared[size_t(t) * width + i], s);
     out[size_t(t) * width + i] = from_f<TB>((base ? to_f(base[size_t(t) * width + i]) : 0.f) + s);
   }
 }
@@ -327,19 +351,21 @@ int launch_expert_linear(const void* x, const void* w, void* out, const int* pla
 
 }  // namespace
 
-// `logits`: float32 scratch [n_tokens, n]
-PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const float* correction, float* logits, int* ids,
+// `logits`: float32 [n_tokens, n + extra]: the router matrix has `extra` more rows whose logits are formed with the
+// others and take no part in the choice (a gate that reads the same input). group_top 1 or 2: a group is scored by its
+// largest choice score or by the sum of its two largest. normalize: weights = scores / (sum of the chosen + 1e-20) * scale.
+PTB_API int ptb_route_grouped(int dtype, const void* h, const float* w_router, const float* correction, float* logits, int* ids,
                       float* gates, int n_tokens, int width, int n, int n_groups, int keep, int top, float route_scale,
-                      int score_kind, cudaStream_t stream) {
+                      int score_kind, int extra, int group_top, int normalize, cudaStream_t stream) {
   if (n_tokens <= 0) return PTB_OK;
   if (n <= 0 || n > 32 * ROUTE_VPL || n_groups <= 0 || n % n_groups != 0 || keep <= 0 || keep > n_groups || top <= 0 ||
-      top > (n / n_groups) * keep || width <= 0 || score_kind < 0 || score_kind > 1)
+      top > (n / n_groups) * keep || width <= 0 || score_kind < 0 || score_kind > 1 || extra < 0 || group_top < 1 || group_top > 2)
     return PTB_ERR_SIZE;
   // few tokens (steps of single tokens): one token a block, so that the blocks fill the device
   const int tpb = n_tokens >= 2 * sm_count() ? ROUTE_TOKENS : 1;
-  dim3 grid((n_tokens + tpb - 1) / tpb, (n + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  dim3 grid((n_tokens + tpb - 1) / tpb, (n + extra + ROUTE_WARPS - 1) / ROUTE_WARPS);
 #define PTB_ROUTE(TT, NTOK) \
-  route_logits_kernel<TT, NTOK><<<grid, 32 * ROUTE_WARPS, 0, stream>>>((const TT*)h, w_router, logits, n_tokens, width, n)
+  route_logits_kernel<TT, NTOK><<<grid, 32 * ROUTE_WARPS, 0, stream>>>((const TT*)h, w_router, logits, n_tokens, width, n + extra)
   if (dtype == PTB_F32) {
     if (tpb == 1) PTB_ROUTE(float, 1);
     else PTB_ROUTE(float, ROUTE_TOKENS);
@@ -353,8 +379,15 @@ PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const flo
   if (launch_status() != PTB_OK) return PTB_ERR_LAUNCH;
   const size_t smem = size_t(ROUTE_WARPS) * (n + n_groups) * sizeof(float);
   route_select_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, 32 * ROUTE_WARPS, smem, stream>>>(
-      logits, correction, ids, gates, n_tokens, n, n_groups, keep, top, route_scale, score_kind);
+      logits, correction, ids, gates, n_tokens, n, n_groups, keep, top, route_scale, score_kind, n + extra, group_top, normalize);
   return launch_status();
+}
+
+PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const float* correction, float* logits, int* ids,
+                      float* gates, int n_tokens, int width, int n, int n_groups, int keep, int top, float route_scale,
+                      int score_kind, cudaStream_t stream) {
+  return ptb_route_grouped(dtype, h, w_router, correction, logits, ids, gates, n_tokens, width, n, n_groups, keep, top,
+                           route_scale, score_kind, 0, 1, 0, stream);
 }
 
 // int32 words of a plan for `pairs` pairs and `max_tiles` tiles
@@ -388,9 +421,10 @@ PTB_API int ptb_expert_linear(int dtype, int mode, const void* x, const void* w,
   return PTB_ERR_DTYPE;
 }
 
-PTB_API int ptb_expert_combine(int dtype, int out_dtype, const void* base, const void* h, const float* y,
+PTB_API int ptb_expert_combine_shared(int dtype, int out_dtype, const void* base, const void* h, const float* y,
                                const int* ids, const float* gates, const int* row_of_pair, void* out, int n_tokens,
-                               int width, int top, cudaStream_t stream) {
+                               int width, int top, const float* shared, const float* shared_gate, int shared_gate_stride,
+                                      cudaStream_t stream) {
   if (n_tokens <= 0) return PTB_OK;
   if (width <= 0 || top <= 0) return PTB_ERR_SIZE;
   const int threads = width >= 1024 ? 256 : 128;
@@ -399,15 +433,24 @@ PTB_API int ptb_expert_combine(int dtype, int out_dtype, const void* base, const
   const dim3 n_tokens_grid(n_tokens, per_token);
   if (dtype == PTB_F32 && out_dtype == PTB_F32)
     expert_combine_kernel<float, float><<<n_tokens_grid, threads, 0, stream>>>(
-        (const float*)base, (const float*)h, y, ids, gates, row_of_pair, (float*)out, width, top);
+        (const float*)base, (const float*)h, y, ids, gates, row_of_pair, (float*)out, width, top, shared, shared_gate,
+        shared_gate_stride);
   else if (dtype == PTB_BF16 && out_dtype == PTB_F32)
     expert_combine_kernel<__nv_bfloat16, float><<<n_tokens_grid, threads, 0, stream>>>(
-        (const float*)base, (const __nv_bfloat16*)h, y, ids, gates, row_of_pair, (float*)out, width, top);
+        (const float*)base, (const __nv_bfloat16*)h, y, ids, gates, row_of_pair, (float*)out, width, top, shared, shared_gate,
+        shared_gate_stride);
   else if (dtype == PTB_BF16 && out_dtype == PTB_BF16)
     expert_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens_grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)base, (const __nv_bfloat16*)h, y, ids, gates, row_of_pair, (__nv_bfloat16*)out, width,
-        top);
+        top, shared, shared_gate, shared_gate_stride);
   else
     return PTB_ERR_DTYPE;
   return launch_status();
+}
+
+PTB_API int ptb_expert_combine(int dtype, int out_dtype, const void* base, const void* h, const float* y,
+                               const int* ids, const float* gates, const int* row_of_pair, void* out, int n_tokens,
+                               int width, int top, cudaStream_t stream) {
+  return ptb_expert_combine_shared(dtype, out_dtype, base, h, y, ids, gates, row_of_pair, out, n_tokens, width, top, nullptr,
+                                   nullptr, 0, stream);
 }

@@ -129,7 +129,7 @@ mlstm_scan_kernel(const T* __restrict__ proj, int stride, const float* __restric
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ gain, const T* __restrict__ gate,
                                       int gate_stride, T* __restrict__ out, int out_stride, int n, int heads, int v_dim,
-                                      float eps) {
+                                      float eps, int gate_silu) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
   if (warp >= n * heads) return;
   const int t = warp / heads, h = warp % heads;
@@ -139,7 +139,10 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ x, const float* 
   const float rstd = 1.0f / sqrtf(warp_sum(ss) / float(v_dim) + eps);
   for (int e = lane; e < v_dim; e += 32) {
     float y = row[e] * rstd * gain[size_t(h) * v_dim + e];
-    if (gate) y *= 1.f / (1.f + expf(-to_f(gate[size_t(t) * gate_stride + size_t(h) * v_dim + e])));
+    if (gate) {
+      const float g = to_f(gate[size_t(t) * gate_stride + size_t(h) * v_dim + e]);
+      y *= (gate_silu ? g : 1.f) / (1.f + expf(-g));      // sigmoid(g), or silu(g) = g sigmoid(g)
+    }
     out[size_t(t) * out_stride + size_t(h) * v_dim + e] = from_f<T>(y);
   }
 }
@@ -198,8 +201,8 @@ PTB_API int ptb_mlstm_state_floats(int heads, int dim, int v_dim) {
 
 // x float32 [n, heads * v_dim]; gain float32 [heads * v_dim]; gate (may be null) and out of `dtype`, rows gate_stride and
 // out_stride apart.
-PTB_API int ptb_head_norm_gate(const float* x, const float* gain, int dtype, const void* gate, int gate_stride, void* out,
-                               int out_stride, int n, int heads, int v_dim, float eps, cudaStream_t stream) {
+PTB_API int ptb_head_norm_gate_act(const float* x, const float* gain, int dtype, const void* gate, int gate_stride, void* out,
+                               int out_stride, int n, int heads, int v_dim, float eps, int gate_silu, cudaStream_t stream) {
   if (n <= 0) return PTB_OK;
   if (heads <= 0 || v_dim <= 0 || out_stride < heads * v_dim) return PTB_ERR_SIZE;
   const long long warps = (long long)n * heads;
@@ -207,11 +210,16 @@ PTB_API int ptb_head_norm_gate(const float* x, const float* gain, int dtype, con
   const unsigned blocks = unsigned((warps * 32 + threads - 1) / threads);
   if (dtype == PTB_F32)
     head_norm_gate_kernel<float><<<blocks, threads, 0, stream>>>(x, gain, (const float*)gate, gate_stride, (float*)out,
-                                                                 out_stride, n, heads, v_dim, eps);
+                                                                 out_stride, n, heads, v_dim, eps, gate_silu);
   else if (dtype == PTB_BF16)
     head_norm_gate_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, gain, (const __nv_bfloat16*)gate, gate_stride,
-                                                                         (__nv_bfloat16*)out, out_stride, n, heads, v_dim, eps);
+                                                                         (__nv_bfloat16*)out, out_stride, n, heads, v_dim, eps, gate_silu);
   else
     return PTB_ERR_DTYPE;
   return launch_status();
+}
+
+PTB_API int ptb_head_norm_gate(const float* x, const float* gain, int dtype, const void* gate, int gate_stride, void* out,
+                               int out_stride, int n, int heads, int v_dim, float eps, cudaStream_t stream) {
+  return ptb_head_norm_gate_act(x, gain, dtype, gate, gate_stride, out, out_stride, n, heads, v_dim, eps, 0, stream);
 }

@@ -380,14 +380,16 @@ class CausalLM:
         if self.position_table is not None:
             # embeddings plus the positions' learned vectors, straight into the float32 stream
             x = k.embed_sum(ctx.dev["tokens"], ctx.dev["tok_pos"], self.embedding, self.position_table, self.status)
-        elif self.spec.stream_float32 and self.embedding_norm is None:
+        elif self.spec.stream_float32 and (self.embedding_norm is None or hasattr(self.embedding_norm, "forward_same")):
             # the stream's first value is formed in float32: the row widened, then scaled, in the gather's kernel
             x = k.embed_rows(ctx.dev["tokens"], self.embedding, self.spec.embedding_scale, self.status)
+            if self.embedding_norm is not None:     # normed in float32, never rounded
+                x = self.embedding_norm.forward_same(x)
         else:
             x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
             if self.spec.embedding_scale != 1.0:
                 k.scale_(x, self.spec.embedding_scale)
-        if self.embedding_norm is not None:
+        if self.embedding_norm is not None and x.dtype != torch.float32:
             x = self.embedding_norm.forward(x)
         if self.spec.stream_float32 and x.dtype != torch.float32:
             x = k.to_float(x)       # from here to the final norm the stream is float32

@@ -16,7 +16,7 @@ from . import native
 
 PAGE = 64  # tokens of a cache page (PTB_PAGE in csrc/common.cuh)
 # names (src/transformers/activations.py:200-228) -> the codes of csrc/common.cuh, the kernels' one table
-ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3, "relu2": 4}   # relu2: relu(x)^2
+ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3, "relu2": 4, "silu": 5}   # relu2: relu(x)^2
 NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
 _ERRORS = {1: "unknown dtype code", 2: "a size that the kernel does not take", 3: "the CUDA launch failed",
            4: "a pointer or row size is not aligned as the kernel needs"}
@@ -101,7 +101,10 @@ def lib():
                      "ptb_linear_attention_chunks_mma", "ptb_linear_attention_token", "ptb_dyt", "ptb_mlstm_gates",
                      "ptb_mlstm_scan", "ptb_mlstm_max_dim", "ptb_mlstm_state_floats", "ptb_head_norm_gate",
                      "ptb_rope_norm_store", "ptb_talk_mix", "ptb_mlstm_chunks", "ptb_mlstm_chunks_supports",
-                     "ptb_mlstm_chunk_tokens", "ptb_embed_rows"):
+                     "ptb_mlstm_chunk_tokens", "ptb_embed_rows", "ptb_attention_generic_capped", "ptb_attention_mma_capped",
+                     "ptb_qk_prepare_store", "ptb_route_grouped", "ptb_expert_combine_shared", "ptb_glu_act",
+                     "ptb_head_norm_gate_act", "ptb_gla_decay", "ptb_gla_walk", "ptb_gla_chunks", "ptb_gla_max_dim",
+                     "ptb_gla_chunk_tokens"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -256,20 +259,23 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                       tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
                       slopes: Optional[torch.Tensor], kv_heads: int, scale: float, window: int = 0,
                       sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
-                      out: Optional[torch.Tensor] = None, keep_first: int = 0, wide: bool = False) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, keep_first: int = 0, wide: bool = False, softcap: float = 0.0,
+                      gate_wide: bool = False) -> torch.Tensor:
     """Causal attention of the step's tokens over the paged cache; returns [tokens, heads * v_dim] (v_dim is
     the V pool's row size). ``sinks`` [heads] float32: one more term exp(sink) in every row's softmax denominator,
     for which nothing is read. ``gate`` [tokens, heads] (a view whose rows may be wider apart): each head's
     output times sigmoid(gate). ``out``: a [tokens, heads * v_dim] view (rows may be wider apart) to write into.
     ``keep_first``: with a window, a sequence's first ``keep_first`` positions stay visible as well. ``wide``: returns
     float32 [tokens, heads, kv_heads, v_dim] instead, every head's softmax weights applied to every K/V head's values
-    (what ``talk_mix`` sums when the heads' weights are mixed after the softmax)."""
+    (what ``talk_mix`` sums when the heads' weights are mixed after the softmax). ``softcap`` > 0: every score becomes
+    softcap * tanh(score / softcap) after the scale. ``gate_wide``: ``gate`` is [tokens, heads * v_dim], a number per
+    entry of the output."""
     _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, sinks)
     n, heads, head_dim = q.shape
     v_dim = v_pool.shape[-1]
     if wide:
-        if gate is not None or sinks is not None or out is not None or out_scale != 1.0:
-            raise KernelError("attention_generic: the wide form takes no sink, gate, factor or output view")
+        if gate is not None or sinks is not None or out is not None or out_scale != 1.0 or softcap:
+            raise KernelError("attention_generic: the wide form takes no sink, gate, factor, cap or output view")
         res = torch.empty((n, heads, kv_heads, v_dim), dtype=torch.float32, device=q.device)
         _check(lib().ptb_attention_generic(_dtype_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), None,
                                            ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
@@ -281,12 +287,13 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
         out = torch.empty((n, heads * v_dim), dtype=q.dtype, device=q.device)
     _check_rows(out, (n, heads * v_dim), q.dtype, "attention_generic: out")
     if gate is not None:
-        _check_rows(gate, (n, heads), q.dtype, "attention_generic: gate")
-    _check(lib().ptb_attention_generic(_dtype_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out),
-                                       ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
-                                       heads, kv_heads, head_dim, ctypes.c_float(scale), window, v_dim, _ptr(sinks),
-                                       _ptr(gate), 0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
-                                       out.stride(0), int(keep_first), None, _stream(q)),
+        _check_rows(gate, (n, heads * v_dim if gate_wide else heads), q.dtype, "attention_generic: gate")
+    _check(lib().ptb_attention_generic_capped(_dtype_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out),
+                                              ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                              heads, kv_heads, head_dim, ctypes.c_float(scale), window, v_dim, _ptr(sinks),
+                                              _ptr(gate), 0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
+                                              out.stride(0), int(keep_first), None, ctypes.c_float(softcap),
+                                              1 if gate_wide else 0, _stream(q)),
            "attention_generic")
     return out
 
@@ -294,14 +301,24 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
 def rope_norm_store(proj: torch.Tensor, bias: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor,
                     batch: StepBatchC, rope, heads: int, kv_heads: int, dim: int, v_dim: int, eps: float,
                     unit_norm: bool = True, v_first: Optional[torch.Tensor] = None, lam: Optional[torch.Tensor] = None,
-                    keep_values: bool = False, write_cache: bool = True):
+                    keep_values: bool = False, write_cache: bool = True, q_gain: Optional[torch.Tensor] = None,
+                    k_gain: Optional[torch.Tensor] = None, norm_first: bool = False, q_temp=None):
     """``proj`` [tokens, >= (heads + kv_heads) dim + kv_heads v_dim] holds q, k, v side by side (rows may lie wider
     apart); ``bias`` (float32, as long) is added in float32. Queries and keys: rotation of a head's first entries by
     ``rope`` = (cos, sin) tables [tokens, pairs] (None: none), then, with ``unit_norm``, division by the head's root mean
     square. Values: ``(1 - lam) v + lam v_first`` where ``v_first`` [tokens, kv_heads v_dim] is given (``lam``: one
     float32 on the device). Keys and values go into the paged pools. Returns q [tokens, heads, dim], and with
-    ``keep_values`` also this layer's own values [tokens, kv_heads v_dim] as they were before any mixing."""
-    _need_cuda(k_pool, v_pool, bias, lam)
+    ``keep_values`` also this layer's own values [tokens, kv_heads v_dim] as they were before any mixing.
+    ``norm_first``: the norm comes before the rotation and multiplies by the gains ``q_gain``, ``k_gain`` (float32 [dim];
+    None: no gains). ``q_temp`` = (coef, every): a query at position p is multiplied by
+    1 + coef ln(floor((p + 1) / every) + 1) at the end."""
+    _need_cuda(k_pool, v_pool, bias, lam, q_gain, k_gain)
+    if (q_gain is not None or k_gain is not None) and not (unit_norm and norm_first):
+        raise KernelError("rope_norm_store: gains go with a norm before the rotation")
+    for g in (q_gain, k_gain):
+        if g is not None and (g.dtype != torch.float32 or g.numel() != dim):
+            raise KernelError("rope_norm_store: gains are float32 [dim]")
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     _check_rows(proj, proj.shape, proj.dtype, "rope_norm_store: proj")
     n = proj.shape[0]
     q = torch.empty((n, heads, dim), dtype=proj.dtype, device=proj.device)
@@ -312,11 +329,12 @@ def rope_norm_store(proj: torch.Tensor, bias: Optional[torch.Tensor], k_pool: to
         _check_rows(v_first, (n, kv_heads * v_dim), proj.dtype, "rope_norm_store: v_first")
         if lam is None or lam.dtype != torch.float32:
             raise KernelError("rope_norm_store: the mixing weight is one float32 on the device")
-    _check(lib().ptb_rope_norm_store(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(bias), _ptr(q), _ptr(k_pool),
-                                     _ptr(v_pool), ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, dim,
-                                     v_dim, ctypes.c_float(eps), 1 if unit_norm else 0, _ptr(v_first),
-                                     0 if v_first is None else v_first.stride(0), _ptr(lam if v_first is not None else None),
-                                     _ptr(kept), 1 if write_cache else 0, _stream(proj)), "rope_norm_store")
+    _check(lib().ptb_qk_prepare_store(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(bias), _ptr(q), _ptr(k_pool),
+                                      _ptr(v_pool), ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, dim,
+                                      v_dim, ctypes.c_float(eps), 1 if unit_norm else 0, _ptr(v_first),
+                                      0 if v_first is None else v_first.stride(0), _ptr(lam if v_first is not None else None),
+                                      _ptr(kept), 1 if write_cache else 0, _ptr(q_gain), _ptr(k_gain), 1 if norm_first else 0,
+                                      ctypes.c_float(coef), every, _stream(proj)), "rope_norm_store")
     return (q, kept) if keep_values else q
 
 
@@ -542,22 +560,23 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, b
                   n_splits: int, scratch: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
                   gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
                   out: Optional[torch.Tensor] = None, wide_weights: bool = False, keep_first: int = 0,
-                  wide: bool = False) -> torch.Tensor:
+                  wide: bool = False, softcap: float = 0.0, gate_wide: bool = False) -> torch.Tensor:
     """Tensor-core attention over the paged cache (bfloat16). A tile holds ``tokens_per_tile`` tokens
     x ``heads_per_tile`` heads of one K/V group in ``warps`` x 16 rows; with ``n_splits`` > 1 the key
     pages are divided among blocks and joined by a second kernel (``scratch``: float32 workspace).
     ``sinks``, ``gate``, ``out_scale``, ``out``: as attention_generic takes them. ``wide_weights``: the softmax
     weights meet the values as two bfloat16 terms (16 bits of mantissa) instead of one. ``keep_first``: with a window,
     the first positions that stay visible left of it. ``wide``: every head's weights on every K/V head's values, float32
-    [tokens, heads, kv_heads, head_dim], as ``attention_generic(wide=True)`` returns them."""
+    [tokens, heads, kv_heads, head_dim], as ``attention_generic(wide=True)`` returns them. ``softcap``, ``gate_wide``: as
+    attention_generic takes them (a gate per entry starts at a whole 32-bit word, rows an even number of entries apart)."""
     _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, scratch, sinks)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_mma takes bfloat16 tensors")
     n, heads, head_dim = q.shape
     out_wide = None
     if wide:
-        if sinks is not None or gate is not None or out_scale != 1.0 or out is not None:
-            raise KernelError("attention_mma: the wide form takes no sink, gate, factor or output view")
+        if sinks is not None or gate is not None or out_scale != 1.0 or out is not None or softcap:
+            raise KernelError("attention_mma: the wide form takes no sink, gate, factor, cap or output view")
         out_wide = torch.empty((n, heads, kv_heads, head_dim), dtype=torch.float32, device=q.device)
     else:
         if out is None:
@@ -566,7 +585,9 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, b
         if out.data_ptr() % 4 or out.stride(0) % 2:
             raise KernelError("attention_mma: output rows must start at whole 32-bit words")
     if gate is not None:
-        _check_rows(gate, (n, heads), q.dtype, "attention_mma: gate")
+        _check_rows(gate, (n, heads * head_dim if gate_wide else heads), q.dtype, "attention_mma: gate")
+        if gate_wide and (gate.data_ptr() % 4 or gate.stride(0) % 2):
+            raise KernelError("attention_mma: a gate per entry must start at whole 32-bit words")
     if n_splits > 1:
         need = attention_mma_scratch_floats(n_tiles, heads, kv_heads, heads_per_tile, n_splits, warps, head_dim)
         if wide:
@@ -575,13 +596,14 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, b
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         elif scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"attention_mma: scratch of {need} float32 values needed")
-    _check(lib().ptb_attention_mma_kept(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
-                                        ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
-                                        heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
-                                        ctypes.c_float(scale), window, _ptr(sinks), _ptr(gate),
-                                        0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
-                                        0 if wide else out.stride(0), 1 if wide_weights else 0, int(keep_first),
-                                        _ptr(out_wide), _stream(q)), "attention_mma")
+    _check(lib().ptb_attention_mma_capped(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
+                                          ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                          heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
+                                          ctypes.c_float(scale), window, _ptr(sinks), _ptr(gate),
+                                          0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
+                                          0 if wide else out.stride(0), 1 if wide_weights else 0, int(keep_first),
+                                          _ptr(out_wide), ctypes.c_float(softcap), 1 if gate_wide else 0, _stream(q)),
+           "attention_mma")
     if n_splits > 1:
         global launches
         launches += 1   # the kernel that joins the splits
@@ -998,39 +1020,52 @@ ROUTE_SCORES = {"softmax": 0, "sigmoid": 1}
 
 
 def route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int, top: int,
-          scale: float, score: str = "softmax"):
+          scale: float, score: str = "softmax", extra: int = 0, group_top: int = 1, normalize: bool = False):
     """Router of a mixture of experts, float32: scores = softmax over all outputs (or a sigmoid per output),
     choice by score + correction (None: no correction) among the ``keep`` best of ``n_groups`` groups,
-    weights = score * scale. Returns (ids int32 [tokens, top], weights float32 [tokens, top])."""
+    weights = score * scale. Returns (ids int32 [tokens, top], weights float32 [tokens, top]).
+
+    ``group_top`` 2: a group is scored by the sum of its two largest choice scores instead of its largest.
+    ``normalize``: weights = score / (sum of the chosen scores + 1e-20) * scale. ``extra``: the last ``extra`` rows of
+    ``w_router`` are no router outputs; their logits are formed with the others (same input, same float32 sums) and the
+    call returns (ids, weights, logits float32 [tokens, outputs + extra])."""
     _need_cuda(h, w_router, correction)
     n_tokens, width = h.shape
-    n = w_router.shape[0]
+    n = w_router.shape[0] - int(extra)
     if (w_router.dtype != torch.float32 or (correction is not None and correction.dtype != torch.float32)
             or w_router.shape[1] != width):
         raise KernelError("route: the router's matrix and correction are float32 [outputs, width] and [outputs]")
     ids = torch.empty((n_tokens, top), dtype=torch.int32, device=h.device)
     gates = torch.empty((n_tokens, top), dtype=torch.float32, device=h.device)
-    logits = torch.empty((n_tokens, n), dtype=torch.float32, device=h.device)
-    _check(lib().ptb_route(_dtype_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(logits), _ptr(ids),
-                           _ptr(gates), n_tokens, width, n, n_groups, keep, top, ctypes.c_float(scale),
-                           ROUTE_SCORES[score], _stream(h)),
+    logits = torch.empty((n_tokens, n + int(extra)), dtype=torch.float32, device=h.device)
+    _check(lib().ptb_route_grouped(_dtype_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(logits), _ptr(ids),
+                                   _ptr(gates), n_tokens, width, n, n_groups, keep, top, ctypes.c_float(scale),
+                                   ROUTE_SCORES[score], int(extra), int(group_top), 1 if normalize else 0, _stream(h)),
            "route")
     global launches
     launches += 1       # the logits and the choice are two kernels
-    return ids, gates
+    return (ids, gates, logits) if extra else (ids, gates)
 
 
 def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_gate_up: torch.Tensor,
                    w_down: torch.Tensor, base: Optional[torch.Tensor] = None, mma_tile_rows: int = 0,
-                   plain_act: Optional[str] = None) -> torch.Tensor:
+                   plain_act: Optional[str] = None, shared: Optional[torch.Tensor] = None,
+                   shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """base + sum over a token's choices of weight * expert(h): experts ``w_gate_up`` [E, 2 F, width]
     (gate rows, then up rows) and ``w_down`` [E, width, F] compute down(silu(gate h) * (up h)); an id >= E
     is an identity expert. Pairs are sorted by expert on the device and run as tiles of grouped
     products. Returns [tokens, width] in ``base``'s dtype (float32 without a base).
 
     With ``plain_act`` (an activation's name) the experts have no gate and take their weight on the input:
-    ``w_gate_up`` is [E, F, width] and the result is base + sum of down(act(up (weight * h)))."""
-    _need_cuda(h, ids, gates, w_gate_up, w_down, base)
+    ``w_gate_up`` is [E, F, width] and the result is base + sum of down(act(up (weight * h))).
+
+    ``shared`` (float32 [tokens, width]): the result of an expert that every token uses, added in the same kernel, times
+    sigmoid(``shared_gate``) where that is given (float32 [tokens, 1], a view whose rows may lie wider apart)."""
+    _need_cuda(h, ids, gates, w_gate_up, w_down, base, shared)
+    if shared is not None and (shared.dtype != torch.float32 or shared.shape != h.shape):
+        raise KernelError("routed_experts: the shared expert's rows are float32 [tokens, width]")
+    if shared_gate is not None and (shared is None or shared_gate.dtype != torch.float32 or shared_gate.shape[0] != h.shape[0]):
+        raise KernelError("routed_experts: the shared expert's gate is one float32 logit per token")
     n_tokens, width = h.shape
     top = ids.shape[1]
     n_experts, two_f, _ = w_gate_up.shape
@@ -1070,9 +1105,10 @@ def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_ga
         raise KernelError("routed_experts: base must have the input's shape, in float32 or the input's dtype")
     out = torch.empty((n_tokens, width), dtype=torch.float32 if base is None else base.dtype, device=h.device)
     row_of_pair = plan[1 + 3 * max_tiles:1 + 3 * max_tiles + pairs]
-    _check(L.ptb_expert_combine(code, _dtype_code(out), _ptr(base), _ptr(h), _ptr(y), _ptr(ids),
-                                _ptr(gates if plain_act is None else None),
-                                _ptr(row_of_pair), _ptr(out), n_tokens, width, top, stream), "expert_combine")
+    _check(L.ptb_expert_combine_shared(code, _dtype_code(out), _ptr(base), _ptr(h), _ptr(y), _ptr(ids),
+                                       _ptr(gates if plain_act is None else None),
+                                       _ptr(row_of_pair), _ptr(out), n_tokens, width, top, _ptr(shared), _ptr(shared_gate),
+                                       0 if shared_gate is None else shared_gate.stride(0), stream), "expert_combine")
     return out
 
 
@@ -1227,6 +1263,16 @@ def glu_clamp(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor
     return out
 
 
+def glu_act(gate_up: torch.Tensor, act: str) -> torch.Tensor:
+    """[rows, 2 F] (gate columns, then up columns) -> [rows, F]: act(gate) * up, with ``act`` a name of ACTIVATIONS."""
+    _need_cuda(gate_up)
+    rows, two_f = gate_up.shape
+    out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().ptb_glu_act(_dtype_code(gate_up), _ptr(gate_up), _ptr(out), rows, two_f // 2, ACTIVATIONS[act],
+                             _stream(gate_up)), "glu_act")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # The Dynamic Tanh norm with the short convolution on a mixer's input; the matrix memory with exponential gates
 DYT_MAX_TAPS = 8
@@ -1330,9 +1376,12 @@ def mlstm(proj: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor, bias_f:
 
 
 def head_norm_gate(x: torch.Tensor, gain: torch.Tensor, gate: Optional[torch.Tensor], heads: int, eps: float,
-                   out_dtype: torch.dtype) -> torch.Tensor:
+                   out_dtype: torch.dtype, gate_act: str = "sigmoid") -> torch.Tensor:
     """Every head's stretch of the float32 rows ``x`` [tokens, heads * v_dim] divided by its root mean square, times
-    ``gain`` [heads * v_dim] times sigmoid(``gate``) (of ``out_dtype``; rows may lie wider apart), in ``out_dtype``."""
+    ``gain`` [heads * v_dim] times sigmoid(``gate``) (of ``out_dtype``; rows may lie wider apart), in ``out_dtype``.
+    ``gate_act`` "silu": times gate * sigmoid(gate) instead."""
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError(f"head_norm_gate: the gate's activation is 'sigmoid' or 'silu', got {gate_act!r}")
     _need_cuda(x, gain)
     n, width = x.shape
     if x.dtype != torch.float32 or width % heads or gain.dtype != torch.float32 or gain.numel() != width:
@@ -1340,7 +1389,57 @@ def head_norm_gate(x: torch.Tensor, gain: torch.Tensor, gate: Optional[torch.Ten
     out = torch.empty((n, width), dtype=out_dtype, device=x.device)
     if gate is not None:
         _check_rows(gate, (n, width), out_dtype, "head_norm_gate: gate")
-    _check(lib().ptb_head_norm_gate(_ptr(x), _ptr(gain), _dtype_code(out), _ptr(gate), 0 if gate is None else gate.stride(0),
-                                    _ptr(out), out.stride(0), n, heads, width // heads, ctypes.c_float(eps), _stream(x)),
+    _check(lib().ptb_head_norm_gate_act(_ptr(x), _ptr(gain), _dtype_code(out), _ptr(gate),
+                                        0 if gate is None else gate.stride(0), _ptr(out), out.stride(0), n, heads,
+                                        width // heads, ctypes.c_float(eps), 1 if gate_act == "silu" else 0, _stream(x)),
            "head_norm_gate")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Gated linear attention: a decay per token and key channel
+GLA_MAX_DIM = 256   # ptb_gla_max_dim()
+GLA_CHUNK = 64      # ptb_gla_chunk_tokens()
+
+
+def gla_decay_(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> torch.Tensor:
+    """In place on float32 rows [tokens, width]: z <- logsigmoid(z + bias) / tau, the logarithm of the decay
+    sigmoid(z + bias) ** (1 / tau). ``bias`` float32 [width] or None."""
+    _need_cuda(z, bias)
+    if z.dtype != torch.float32 or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != z.shape[1])):
+        raise KernelError("gla_decay_ takes float32 rows and a float32 bias of their width")
+    _check(lib().ptb_gla_decay(_ptr(z), _ptr(bias), z.shape[0], z.shape[1], ctypes.c_float(tau), _stream(z)), "gla_decay")
+    return z
+
+
+def gla(proj: torch.Tensor, log_decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, heads: int,
+        dim: int, v_dim: int, q_scale: float, chunks=None) -> torch.Tensor:
+    """Per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t * q_scale) over the step's tokens, continuing and
+    leaving each sequence's S [heads, dim, v_dim] in ``state`` [slots, heads * dim * v_dim] (float32; rows may lie wider
+    apart). ``proj`` [tokens, >= 2 heads dim + heads v_dim] holds q, k, v side by side (rows may lie wider apart);
+    ``log_decay`` float32 [tokens, heads * dim] the logarithms of the decays a_t. ``chunks``: (chunk_seq, chunk_q0,
+    seq_chunk0, n_chunks) for the chunked form (prompts), None to walk every sequence token by token. Returns float32
+    [tokens, heads * v_dim]."""
+    _need_cuda(log_decay, slots)
+    n = proj.shape[0]
+    if state.dtype != torch.float32 or state.shape[1] != heads * dim * v_dim or state.stride(1) != 1:
+        raise KernelError("gla: the state is float32 [slots, heads * dim * v_dim]")
+    if log_decay.dtype != torch.float32 or tuple(log_decay.shape) != (n, heads * dim):
+        raise KernelError("gla: the decays' logarithms are float32 [tokens, heads * dim]")
+    _check_rows(proj, proj.shape, proj.dtype, "gla: proj")
+    out = torch.empty((n, heads * v_dim), dtype=torch.float32, device=proj.device)
+    if chunks is None:
+        _check(lib().ptb_gla_walk(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(log_decay), _ptr(state), state.stride(0),
+                                  _ptr(slots), ctypes.byref(batch), _ptr(out), heads, dim, v_dim, ctypes.c_float(q_scale),
+                                  _stream(proj)), "gla_walk")
+        return out
+    chunk_seq, chunk_q0, seq_chunk0, n_chunks = chunks
+    sums = torch.empty((n_chunks, heads, dim, v_dim), dtype=torch.float32, device=proj.device)
+    decays = torch.empty((n_chunks, heads, dim), dtype=torch.float32, device=proj.device)
+    _check(lib().ptb_gla_chunks(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(log_decay), _ptr(state), state.stride(0),
+                                _ptr(slots), ctypes.byref(batch), _ptr(chunk_seq), _ptr(chunk_q0), _ptr(seq_chunk0), n_chunks,
+                                _ptr(sums), _ptr(decays), _ptr(out), heads, dim, v_dim, ctypes.c_float(q_scale),
+                                _stream(proj)), "gla_chunks")
+    global launches
+    launches += 2       # three kernels
     return out

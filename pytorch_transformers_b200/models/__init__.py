@@ -8,6 +8,8 @@ from ..config.zalunex import ZalunexConfig
 from .zalunex import zalunex_spec
 from ..config.pogezen import PogezenConfig
 from .pogezen import pogezen_spec
+from ..config.figudra import FigudraConfig
+from .figudra import figudra_spec
 
 register_architecture(
     "falcon", ("FalconForCausalLM", "RWForCausalLM"), FalconConfig, falcon_spec, name_rules=FALCON_NAME_RULES,
@@ -16,3 +18,4 @@ register_architecture(
 register_architecture("pafevik", ("Pafevik",), PafevikConfig, pafevik_spec)
 register_architecture("zalunex", ("Zalunex",), ZalunexConfig, zalunex_spec)
 register_architecture("pogezen", ("Pogezen",), PogezenConfig, pogezen_spec)
+register_architecture("figudra", ("Figudra",), FigudraConfig, figudra_spec)

@@ -4,7 +4,8 @@
 output is ``(x + mixer) + ff``, each sum formed in float32 in the epilogue of the kernel that
 produces the second term; the reference adds in the order ``x + (ff + mixer)`` (FalconDecoderLayer with parallel attention,
 src/transformers/models/falcon/modeling_falcon.py:630-634, 652-654, 673-676); with a
-``norm_ff`` child the feed-forward has its own norm of x, else it shares the mixer's.
+``norm_ff`` child the feed-forward has its own norm of x, else it shares the mixer's; without a ``feed_forward`` child
+the block is ``x + mixer``.
 ``sequential``: ``r = x + mixer(norm(x))``, then ``r + ff(norm_ff(r))`` (:656-659, 676); without a
 ``feed_forward`` child the block ends at ``r``.
 Sums are formed in float32 and rounded once; where the model keeps its residual stream in float32
@@ -35,12 +36,12 @@ class ParallelBlock(Part):
         self.norm_mixer = self.children["norm_mixer"]
         self.norm_ff = self.children.get("norm_ff")
         self.mixer = self.children["mixer"]
-        self.feed_forward = self.children["feed_forward"]
+        self.feed_forward = self.children.get("feed_forward")     # a block without one is x + mixer(norm(x))
 
     def forward(self, x, ctx, entry):
         k = self.build.kernels
         side = getattr(ctx, "side_stream", None)
-        two_streams = (side is not None and getattr(self.mixer, "fuses_add", False)
+        two_streams = (side is not None and self.feed_forward is not None and getattr(self.mixer, "fuses_add", False)
                        and getattr(self.feed_forward, "fuses_add", False) and hasattr(self.norm_mixer, "forward_sum"))
         can_join = hasattr(self.norm_mixer, "forward_sum")
         if isinstance(x, DeferredSum) and can_join:
@@ -60,6 +61,8 @@ class ParallelBlock(Part):
         if two_streams:
             return self._forward_two_streams(x, a, m, ctx, entry, side)
         mixed = _plus(k, self.mixer, x, a, ctx, entry)           # x + mixer
+        if self.feed_forward is None:
+            return mixed
         # (x + mixer) + feed-forward: the last sum is left to whoever needs the value (the next
         # block's norm adds and norms in one kernel; the model's end adds)
         return DeferredSum(mixed, self.feed_forward.forward(m, ctx))

@@ -12,6 +12,11 @@ Variants, all by constructor parameters: ``score="sigmoid"`` scores every output
 instead of the softmax; ``correction=False`` has no correction tensor; ``expert="plain"`` experts have no
 gate, ``W_down act(W_up h)`` with ``activation`` by name; ``weight_on="input"`` multiplies the expert's
 input by the weight instead of its output: the result is the sum of ``expert(weight * h)``.
+``group_score="top2_sum"`` scores a group by the sum of its two largest choice scores instead of its largest.
+``normalize=True`` divides the chosen outputs' scores by their sum (+ 1e-20) before ``scale``. A ``shared`` child (a
+feed-forward part that returns float32 sums) is an expert that every token uses; its result is added in the kernel
+that sums the chosen experts, and with ``shared_gate=True`` it is multiplied by ``sigmoid(w_sg . h)``, one number per
+token whose row ``shared_gate`` [1, hidden] is held with the router's matrix and multiplied with it (float32).
 """
 from __future__ import annotations
 
@@ -30,8 +35,15 @@ class RoutedExperts(Part):
     def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, inner: int, experts: int, top: int,
                  identity: int = 0, groups: int = 1, keep: int = 1, scale: float = 1.0, score: str = "softmax",
                  correction: bool = True, expert: str = "gated_silu", activation: str = "gelu",
-                 weight_on: str = "output"):
+                 weight_on: str = "output", group_score: str = "max", normalize: bool = False, shared_gate: bool = False):
         super().__init__(build, spec)
+        if group_score not in ("max", "top2_sum"):
+            raise ValueError(f"a group's score is 'max' or 'top2_sum', got {group_score!r}")
+        self.group_score, self.normalize = group_score, bool(normalize)
+        self.shared = self.children.get("shared")
+        self.has_shared_gate = bool(shared_gate)
+        if self.has_shared_gate and self.shared is None:
+            raise ValueError("shared_gate needs a shared expert (a child part 'shared')")
         if score not in build.kernels.ROUTE_SCORES:
             raise ValueError(f"router scores are one of {', '.join(build.kernels.ROUTE_SCORES)}, got {score!r}")
         if expert not in ("gated_silu", "plain") or weight_on not in ("output", "input"):
@@ -58,6 +70,8 @@ class RoutedExperts(Part):
         d = {"router": ParamDecl((n, self.hidden), role="vector")}
         if self.has_correction:
             d["correction"] = ParamDecl((n,), role="vector")
+        if self.has_shared_gate:
+            d["shared_gate"] = ParamDecl((1, self.hidden), role="vector")
         for e in range(self.experts):
             if self.expert == "gated_silu":
                 d[f"e{e}.gate"] = ParamDecl((self.inner, self.hidden))
@@ -67,6 +81,8 @@ class RoutedExperts(Part):
 
     def bind(self, t: Dict[str, torch.Tensor]) -> None:
         self.p_router, self.p_correction = t["router"].contiguous(), t.get("correction")
+        if self.has_shared_gate:        # one more row of the router's product: the shared expert's gate
+            self.p_router = torch.cat([self.p_router, t["shared_gate"].reshape(1, self.hidden)]).contiguous()
         E, F = self.experts, self.inner
         if self.expert == "plain":      # [E, F, hidden] and [E, hidden, F]
             self.p_gate_up = torch.stack([t.pop(f"e{e}.up") for e in range(E)]).contiguous()
@@ -85,7 +101,15 @@ class RoutedExperts(Part):
         k = self.build.kernels
         if callable(add):
             add = add()
-        ids, weights = k.route(x, self.p_router, self.p_correction, self.groups, self.keep, self.top, self.scale,
-                               self.score)
+        routed = k.route(x, self.p_router, self.p_correction, self.groups, self.keep, self.top, self.scale, self.score,
+                         extra=1 if self.has_shared_gate else 0, group_top=2 if self.group_score == "top2_sum" else 1,
+                         normalize=self.normalize)
+        ids, weights = routed[0], routed[1]
+        shared = shared_gate = None
+        if self.shared is not None:
+            shared = self.shared.forward(x, ctx)        # float32 sums of the shared expert's last product
+            if self.has_shared_gate:
+                shared_gate = routed[2][:, self.experts + self.identity:]
         return k.routed_experts(x, ids, weights, self.p_gate_up, self.p_down, base=add,
-                                plain_act=self.activation if self.expert == "plain" else None)
+                                plain_act=self.activation if self.expert == "plain" else None, shared=shared,
+                                shared_gate=shared_gate)

@@ -1,6 +1,7 @@
 """Feed-forward parts. ``dense``: down(act(up(x))), no gating
 (FalconMLP, src/transformers/models/falcon/modeling_falcon.py:565-578; activations by name,
-src/transformers/activations.py:200-228)."""
+src/transformers/activations.py:200-228). ``gated``: down(act(gate(x)) * up(x)) with the activation by name.
+``clamped_glu``: a gated unit with clamped branches."""
 from __future__ import annotations
 
 from typing import Dict
@@ -76,3 +77,44 @@ class ClampedGatedFeedForward(Part):
         k = self.build.kernels
         y = k.glu_clamp(linear(k, x, self.p_gate_up), self.limit, self.alpha)
         return linear(k, y, self.p_down, wide_out=self.wide_out)
+
+
+@register_part("feed_forward", "gated")
+class GatedFeedForward(Part):
+    """y = W_down (act(W_gate x) * (W_up x)), ``activation`` by name (the tanh form of GELU, silu, ...). Gate and up are
+    one matrix and one product; the unit between the products is one kernel. With ``wide_out`` the last product's
+    float32 sums are returned unrounded (for a float32 stream, or for a kernel that weighs and adds them)."""
+    graph_safe = True
+    fuses_add = True
+
+    def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, inner: int, activation: str = "silu",
+                 wide_out: bool = False):
+        super().__init__(build, spec)
+        if activation not in build.kernels.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not supported "
+                             f"(supported: {', '.join(build.kernels.ACTIVATIONS)})")
+        self.hidden, self.inner, self.activation, self.wide_out = int(hidden), int(inner), activation, bool(wide_out)
+        self.p_gate_up = self.p_down = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {"gate": ParamDecl((self.inner, self.hidden)), "up": ParamDecl((self.inner, self.hidden)),
+                "down": ParamDecl((self.hidden, self.inner))}
+
+    def bind(self, t) -> None:
+        import torch
+        self.p_gate_up = torch.cat([t["gate"], t["up"]]).contiguous()
+        self.p_down = t["down"]
+
+    def forward(self, x, ctx, add=None):
+        k = self.build.kernels
+        y = k.glu_act(linear(k, x, self.p_gate_up), self.activation)
+        if callable(add):
+            add = add()
+        if add is not None:
+            return linear(k, y, self.p_down, add=add)
+        return linear(k, y, self.p_down, wide_out=self.wide_out)
+
+    def forward_pending(self, x, ctx):
+        """The result as the last product's float32 sums (and no bias), for a kernel that adds them to the stream later."""
+        k = self.build.kernels
+        return linear_pending(k, k.glu_act(linear(k, x, self.p_gate_up), self.activation), self.p_down)

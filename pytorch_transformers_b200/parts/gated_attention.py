@@ -6,7 +6,13 @@
 * a sliding window: position i sees j with 0 <= i - j < window (0: all earlier positions);
 * a sink: one learned logit per head that takes part in the softmax's normalisation only: ``exp(sink)`` is one
   more term of the denominator, used as stored (``scale`` does not touch it), and nothing is read for it;
-* an output gate: head h's result times sigmoid(W_g x)_h, one number per head, read from the mixer's input;
+* an output gate: head h's result times sigmoid(W_g x)_h, one number per head, read from the mixer's input; with
+  ``gate_wide`` W_g has heads * vdim rows and every entry of the concatenated heads has a gate of its own;
+* a sink of a fixed value instead of a learned one (``sink_value``; 0 adds one to every softmax's denominator);
+* a soft cap on the scores (``softcap``): score <- softcap * tanh(score / softcap) after the scale;
+* a query temperature (``q_temp`` = (coef, every)): the query at position p is multiplied by
+  1 + coef ln(floor((p + 1) / every) + 1);
+* a norm with gains that comes before the rotation (``norm_first``);
 * values of a size of their own (``vdim``);
 * biases on the four projections (``bias``), added in float32 where queries, keys and values are laid out;
 * a rotation of queries and keys from a ``position`` child, applied before the norm of queries and keys, and a
@@ -41,7 +47,8 @@ class SinkAttention(Part):
     def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int,
                  scale: float, window: int = 0, eps: float = 1e-6, qk_norm: bool = True, sink: bool = True,
                  gate: bool = True, bias: bool = False, qk_gain: bool = True, keep_first: int = 0, talk: bool = False,
-                 value_mix: str = "none", value_mix_key: str = "values"):
+                 value_mix: str = "none", value_mix_key: str = "values", softcap: float = 0.0, q_temp=None,
+                 gate_wide: bool = False, sink_value=None, norm_first: bool = False):
         super().__init__(build, spec)
         if heads % kv_heads:
             raise ValueError(f"heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
@@ -58,10 +65,25 @@ class SinkAttention(Part):
         if self.talk and (self.has_sink or self.has_gate):
             raise ValueError("mixed softmax weights go with neither a sink nor an output gate")
         self.value_mix, self.value_mix_key = value_mix, str(value_mix_key)
+        self.softcap, self.gate_wide, self.norm_first = float(softcap or 0.0), bool(gate_wide), bool(norm_first)
+        self.q_temp = None if not q_temp else (float(q_temp[0]), int(q_temp[1]))
+        self.sink_value = None if sink_value is None else float(sink_value)
+        if self.softcap < 0 or (self.q_temp is not None and self.q_temp[1] <= 0):
+            raise ValueError("softcap must not be negative and q_temp's period must be positive")
+        if self.sink_value is not None and self.has_sink:
+            raise ValueError("a sink is learned (sink=True) or has a fixed value (sink_value), not both")
+        if self.gate_wide and not self.has_gate:
+            raise ValueError("gate_wide needs gate=True")
+        if self.talk and (self.softcap or self.sink_value is not None):
+            raise ValueError("mixed softmax weights go with neither a sink nor a soft cap")
+        if self.norm_first and not (self.qk_norm and self.qk_gain):
+            raise ValueError("norm_first is the norm with gains before the rotation (qk_norm and qk_gain)")
+        self.gate_cols = (self.heads * self.vdim if self.gate_wide else self.heads) if self.has_gate else 0
         self.position = self.children.get("position")
         # the second path: rotation, biases, kept first positions, mixed weights or mixed values
         self.extended = bool(self.position is not None or self.has_bias or self.keep_first or self.talk
-                             or self.value_mix != "none" or (self.qk_norm and not self.qk_gain))
+                             or self.value_mix != "none" or (self.qk_norm and not self.qk_gain) or self.norm_first
+                             or self.q_temp is not None)
         self.p_in = self.p_o = self.p_q_norm = self.p_k_norm = self.p_sink = None
         self.p_in_b = self.p_o_b = self.p_talk = self.p_vmix = None
 
@@ -75,12 +97,12 @@ class SinkAttention(Part):
         if self.has_sink:
             decls["sink"] = ParamDecl((H,), role="vector", std=1.0)
         if self.has_gate:
-            decls["g"] = ParamDecl((H, self.hidden))
+            decls["g"] = ParamDecl((self.gate_cols, self.hidden))
         if self.has_bias:
             decls.update({"q_b": ParamDecl((H * d,), role="vector", std=0.5), "k_b": ParamDecl((G * d,), role="vector", std=0.5),
                           "v_b": ParamDecl((G * vd,), role="vector", std=0.5), "o_b": ParamDecl((self.hidden,), role="vector")})
             if self.has_gate:
-                decls["g_b"] = ParamDecl((H,), role="vector")
+                decls["g_b"] = ParamDecl((self.gate_cols,), role="vector")
         if self.talk:
             decls["talk"] = ParamDecl((H, H), role="vector", std=0.5)
         if self.value_mix != "none":
@@ -92,6 +114,8 @@ class SinkAttention(Part):
         self.p_in = torch.cat(rows).contiguous()
         self.p_o = t["o"]
         self.p_q_norm, self.p_k_norm, self.p_sink = t.get("q_norm"), t.get("k_norm"), t.get("sink")
+        if self.sink_value is not None:
+            self.p_sink = torch.full((self.heads,), self.sink_value, dtype=torch.float32, device=t["q"].device)
         if self.has_bias:
             self.p_in_b = torch.cat([t["q_b"], t["k_b"], t["v_b"]] + ([t["g_b"]] if self.has_gate else [])).contiguous()
             self.p_o_b = t["o_b"]
@@ -99,7 +123,7 @@ class SinkAttention(Part):
 
     # ---- the projected protocol (parts/pair.py)
     def in_rows(self) -> int:
-        return (self.heads + self.kv_heads) * self.dim + self.kv_heads * self.vdim + (self.heads if self.has_gate else 0)
+        return (self.heads + self.kv_heads) * self.dim + self.kv_heads * self.vdim + self.gate_cols
 
     def out_columns(self) -> int:
         return self.heads * self.vdim
@@ -132,10 +156,11 @@ class SinkAttention(Part):
             return self._forward_extended(proj, ctx, entry, out, out_scale, k_pool, v_pool, batch)
         q = k.qk_norm_store(proj, k_pool, v_pool, batch, self.p_q_norm, self.p_k_norm, self.heads, self.kv_heads, self.dim,
                             self.vdim, self.eps, write_cache=entry.writes_cache)
-        gate = proj[:, self.in_rows() - self.heads:] if self.has_gate else None
+        gate = proj[:, self.in_rows() - self.gate_cols:] if self.has_gate else None
         tiles = ctx.plan(AttentionTiles.plan_key)
+        extras = {"softcap": self.softcap, "gate_wide": self.gate_wide}
         if (q.dtype == torch.bfloat16 and self.dim == self.vdim and k.attention_mma_supports(self.dim)
-                and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+                and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0 and self._gate_fits_mma(gate)):
             # bfloat16 with a head size of the tensor-core kernel: tiles of tokens x heads of a K/V group; a step of
             # single tokens divides each sequence's visible pages among blocks that a second kernel joins
             tokens = tiles.facts["mma_tokens"]
@@ -148,36 +173,45 @@ class SinkAttention(Part):
                 hpk = max(1, min(q_per_kv, 128 // tokens))
             k.attention_mma(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"], tiles.facts["n_mma_tiles"],
                             None, self.kv_heads, self.scale, self.window, tokens, hpk, warps, splits, sinks=self.p_sink,
-                            gate=gate, out_scale=out_scale, out=out, wide_weights=True)
+                            gate=gate, out_scale=out_scale, out=out, wide_weights=True, **extras)
             return
         k.attention_generic(q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"], tiles.facts["n_tiles"],
                             None, self.kv_heads, self.scale, self.window, sinks=self.p_sink, gate=gate, out_scale=out_scale,
-                            out=out)
+                            out=out, **extras)
+
+    def _gate_fits_mma(self, gate) -> bool:
+        """A gate per entry is read two entries at a time by the tensor-core kernel: whole 32-bit words."""
+        return gate is None or not self.gate_wide or (gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0)
 
     def _forward_extended(self, proj, ctx, entry, out, out_scale, k_pool, v_pool, batch) -> None:
         k = self.build.kernels
-        if self.qk_norm and self.qk_gain:
+        if self.qk_norm and self.qk_gain and not self.norm_first:
             raise ValueError("sink_attention: a rotation, biases, kept first positions, mixed weights or mixed values go "
-                             "with a norm of queries and keys without gains (qk_gain=False) or none")
+                             "with a norm of queries and keys without gains (qk_gain=False), with one before the rotation "
+                             "(norm_first=True) or with none")
         if self.has_gate and self.has_bias:
             raise ValueError("sink_attention: an output gate with a bias is not built")
         H, G, d, vd = self.heads, self.kv_heads, self.dim, self.vdim
         first = ctx.shared.get(self.value_mix_key) if self.value_mix == "mix" else None
         if self.value_mix == "mix" and first is None:
             raise ValueError(f"sink_attention: no earlier layer of this step left values under {self.value_mix_key!r}")
-        res = k.rope_norm_store(proj, self.p_in_b, k_pool, v_pool, batch, ctx.rope(self.position), H, G, d, vd, self.eps,
+        rope = ctx.rope(self.position) if self.position is not None else None
+        res = k.rope_norm_store(proj, self.p_in_b, k_pool, v_pool, batch, rope, H, G, d, vd, self.eps,
                                 unit_norm=self.qk_norm, v_first=first, lam=self.p_vmix, keep_values=self.value_mix == "source",
-                                write_cache=entry.writes_cache)
+                                write_cache=entry.writes_cache, q_gain=self.p_q_norm if self.norm_first else None,
+                                k_gain=self.p_k_norm if self.norm_first else None, norm_first=self.norm_first,
+                                q_temp=self.q_temp)
         if self.value_mix == "source":
             q, ctx.shared[self.value_mix_key] = res
         else:
             q = res
         tiles = ctx.plan(AttentionTiles.plan_key)
-        gate = proj[:, self.in_rows() - H:] if self.has_gate else None
+        gate = proj[:, self.in_rows() - self.gate_cols:] if self.has_gate else None
+        extras = {"softcap": self.softcap, "gate_wide": self.gate_wide}
         if self.talk and out_scale != 1.0:
             raise ValueError("sink_attention: mixed softmax weights take no output factor")
         if (q.dtype == torch.bfloat16 and d == vd and k.attention_mma_supports(d) and out.stride(0) % 2 == 0
-                and out.data_ptr() % 4 == 0):
+                and out.data_ptr() % 4 == 0 and self._gate_fits_mma(gate)):
             # the tensor-core kernel, tiled as in forward_projected; with mixed weights a block forms one K/V group's
             # weights on one K/V head's values, float32, and talk_mix sums them
             tokens, q_per_kv = tiles.facts["mma_tokens"], H // G
@@ -194,14 +228,15 @@ class SinkAttention(Part):
                            q.dtype, out=out)
             else:
                 k.attention_mma(*margs, sinks=self.p_sink, gate=gate, out_scale=out_scale, out=out, wide_weights=True,
-                                keep_first=self.keep_first)
+                                keep_first=self.keep_first, **extras)
             return
         args = (q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"], tiles.facts["n_tiles"], None, G,
                 self.scale, self.window)
         if self.talk:
             k.talk_mix(k.attention_generic(*args, keep_first=self.keep_first, wide=True), self.p_talk, q.dtype, out=out)
             return
-        k.attention_generic(*args, sinks=self.p_sink, gate=gate, out_scale=out_scale, out=out, keep_first=self.keep_first)
+        k.attention_generic(*args, sinks=self.p_sink, gate=gate, out_scale=out_scale, out=out, keep_first=self.keep_first,
+                            **extras)
 
     def _decode_splits(self, ctx, hpk: int, value_heads: int = 1) -> int:
         """Blocks per (sequence, K/V head) in a step of single tokens: enough to fill the device, each with two

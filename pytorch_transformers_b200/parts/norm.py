@@ -39,6 +39,11 @@ class LayerNorm(Part):
             return self.build.kernels.norm_stream(x, self.p_weight, self.p_bias, self.eps, self.kind, self.build.dtype)
         return self.build.kernels.norm(x, self.p_weight, self.p_bias, self.eps, self.kind)
 
+    def forward_same(self, x):
+        """The norm in ``x``'s own dtype: a float32 stream stays float32 (the norm of the embeddings, which is the
+        stream's first value)."""
+        return self.build.kernels.norm(x, self.p_weight, self.p_bias, self.eps, self.kind)
+
     def forward_sum(self, x, addend, other: "LayerNorm" = None):
         """Norm of ``x + addend``: returns (the sum, its norm[, ``other``'s norm of it]) from one kernel."""
         k = self.build.kernels

@@ -41,6 +41,12 @@ class WeightError(RuntimeError):
         super().__init__("\n".join(lines))
 
 
+def _fits(stored, wanted) -> bool:
+    """Does a stored shape fit a declared one? A declared size of -1 is whatever the checkpoint holds (a size that
+    no configuration key gives, only the tensor itself)."""
+    return len(stored) == len(wanted) and all(w == -1 or int(s) == int(w) for s, w in zip(stored, wanted))
+
+
 def checkpoint_dtype(folder: str) -> Optional[torch.dtype]:
     """The dtype that the folder's archives store their matrices in: float32 if the first floating-point
     tensor of two or more dimensions is stored in 32-bit, bfloat16 if it is stored in 16 bits (bfloat16 or
@@ -88,7 +94,7 @@ def load_weights(model, folder: str, name_rules: Optional[dict] = None, strict: 
             e = f.entries[real]
             if tuple(decl.shape) == () and tuple(e.shape) == (1,):
                 pass        # a scalar stored as one element
-            elif tuple(e.shape) != tuple(decl.shape):
+            elif not _fits(e.shape, decl.shape):
                 mismatched.append(f"{name}: stored {list(e.shape)}, model wants {list(decl.shape)}")
             elif decl.role == "int" and e.dtype.is_floating_point:
                 mismatched.append(f"{name}: stored as {e.dtype}, model wants an integer table")

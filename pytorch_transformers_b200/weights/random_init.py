@@ -31,6 +31,9 @@ def random_tensor(name: str, decl, seed: int, device, dtype: torch.dtype,
     of ``store_dtype`` (default: ``dtype``) holds. On a CUDA device the fill kernel writes the
     tensor in place (no float32 staging copy); elsewhere the host generator does."""
     device = torch.device(device)
+    if any(int(n) < 0 for n in decl.shape):
+        raise ValueError(f"{name}: a size that only a checkpoint's tensor gives ({list(decl.shape)}) cannot be drawn at "
+                         "random; give it in the configuration")
     if decl.role == "int" or decl.init == "zeros":
         return torch.zeros(decl.shape, dtype=torch.int32 if decl.role == "int" else dtype, device=device)
     if decl.init not in _LAWS:
