@@ -1,11 +1,11 @@
 """pytorch_transformers_b200: a small model library with generation of its own for one NVIDIA
 B200 (sm_100a): typed configuration and registry, safetensors weights, models put together from
 parts, a paged cache, one step function, a generation loop, sampling, trace replay.
-Architectures built: Falcon, Pafevik, Zalunex, Pogezen."""
+Architectures built: Falcon, Pafevik, Zalunex, Pogezen, Figudra."""
 from . import models  # noqa: F401  (registers the built-in architectures)
 from .cache.paged import Cache
 from .cache.pool import CacheError, CacheFull
-from .config import (AutoConfig, ConfigError, FalconConfig, GenerationConfig, ModelConfig, PafevikConfig,
+from .config import (AutoConfig, ConfigError, FalconConfig, FigudraConfig, GenerationConfig, ModelConfig, PafevikConfig,
                      PogezenConfig, ZalunexConfig, register_architecture)
 from .engine.batch import StepError
 from .engine.model import CausalLM
