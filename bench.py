@@ -572,7 +572,7 @@ class KernelTimes:
              "latent_unfolded_attention",
              "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_",
              "embed_sum", "post_norm_add", "qk_norm_store", "linear_attention", "norm_gate", "glu_clamp", "softcap_",
-             "dyt", "mlstm", "head_norm_gate", "rope_norm_store", "talk_mix", "embed_rows")
+             "dyt", "mlstm", "head_norm_gate", "rope_norm_store", "talk_mix", "embed_rows", "gla", "gla_decay_", "glu_act")
 
     def __init__(self, kernels):
         self.k, self.records, self.saved = kernels, [], {}
@@ -950,8 +950,127 @@ def run_pogezen(args):
     print(json.dumps(result))
     return 0
 
+# ---- Figudra beside Zalunex at equal size (`--only figudra [--size s|m]`) ----
+# Sizes that resemble a served model's layers: the width; four parallel layers: an attention of 16 or 32 heads of 128 on a
+# quarter as many K/V heads with normed and partly rotated queries and keys, a window of 1,024 that keeps the first 4
+# tokens and one added to the softmax's denominator, over a gated GELU unit 4 x the width wide; a gated linear attention
+# of as many heads of 128 x 128 whose decays come through a rank of 64, over 64 experts of 1,408 of which a token uses 6
+# (in 4 of 8 groups) and a shared expert of 2,816; a full attention with a query temperature, capped scores and a gate
+# per entry over the same experts; a gated linear attention over the gated unit. Zalunex beside it is `--only zalunex`'s
+# model of the same width, heads, layers and experts: the library's other design with a float32 stream, a windowed
+# attention with a sink and a gate, a linear attention with a state per head and routed experts.
+def figudra_config(size):
+    z = PAFEVIK_SIZES[size]
+    w, heads = z["width"], z["heads"]
+    win = {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "mask": {"size": 1024, "keep_first": 4}, "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0}}}
+    full = {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+            "q_temp": {"coef": 0.5, "every": 512}}
+    lin = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 64}
+    glu = {"kind": "dense", "ff": 4 * w}
+    moe = {"kind": "moe", "expert": {"ff": 1408}, "shared": {"ff": 2816},
+           "router": {"experts": 64, "top": 6, "scale": 2.0, "groups": {"count": 8, "keep": 4}}}
+    return {"architecture": "Figudra", "vocab": 32000, "width": w, "norm": {"eps": 1e-6},
+            "layers": [{"type": t, "mixer": dict(m), "mlp": f} for t, m, f in
+                       (("attention_2", win, glu), ("gla", lin, moe), ("attention", full, moe), ("gla", lin, glu))]}
+
+
+def run_figudra(args):
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+    tokens, batch, context = args.prefill_tokens, args.batch, args.context
+    raw = figudra_config(args.size)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    win, lin, w = raw["layers"][0]["mixer"], raw["layers"][1]["mixer"], raw["width"]
+    result = {"only": "figudra", "size": args.size, "prefill_tokens": tokens, "batch": batch, "context": context,
+              "config": {"width": w, "layers": len(raw["layers"]), "heads": win["heads"]}}
+    for name, make in (("figudra", lambda: ptb.AutoModelForCausalLM.from_config(ptb.FigudraConfig.from_dict(raw), seed=0, dtype="bfloat16")),
+                       ("zalunex", lambda: ptb.AutoModelForCausalLM.from_config(ptb.ZalunexConfig.from_dict(zalunex_config(args.size)),
+                                                                               seed=0, dtype="bfloat16"))):
+        model = make()
+        result[name] = measure_prefill_and_decode(model, args, gen, flush)
+        del model
+        torch.cuda.empty_cache()
+    F, Z = result["figudra"], result["zalunex"]
+
+    def per_call(table, key):
+        return table[key]["ms"] / table[key]["calls"] if key in table else None
+
+    roof = {}
+    H, G, d, vd = win["heads"], win["kv_heads"], win["dim"], win["vdim"]
+    keep, size = win["mask"]["keep_first"], win["mask"]["size"]
+    seen = sum(min(t + 1, size) + max(0, min(keep, t + 1 - size)) for t in range(tokens))     # pairs the windowed layer sees
+    full = tokens * (tokens + 1) // 2                                                         # pairs the full layer sees
+    zl, zr = zalunex_config(args.size)["layers"][0]["mixer"]["left"], zalunex_config(args.size)["layers"][0]["mixer"]["right"]
+    zseen = sum(min(t_ + 1, zl["mask"]["size"]) for t_ in range(tokens))
+    for key in ("attention_generic", "attention_mma"):
+        t = F["prefill_kernels_ms"].get(key)
+        if t:   # one windowed layer and one full layer share the kernel and the table's row
+            roof[f"{key}_prefill_TFLOPs"] = round(H * (seen + full) * 2 * (d + vd) / t["ms"] / 1e9, 1)
+            roof[f"{key}_prefill_frac_of_burst"] = round(roof[f"{key}_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+        t = per_call(Z["prefill_kernels_ms"], key)
+        if t:
+            roof[f"zalunex_{key}_prefill_TFLOPs"] = round(zl["heads"] * zseen * 2 * (zl["dim"] + zl["vdim"]) / t / 1e9, 1)
+            roof[f"zalunex_{key}_prefill_frac_of_burst"] = round(roof[f"zalunex_{key}_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    lh, ld, lv = lin["heads"], lin["dim"], lin["vdim"]
+    t = per_call(F["prefill_kernels_ms"], "gla")
+    if t:   # q, k, v and the decays' logarithms in, float32 rows out; per token and head: own sum, outputs, state
+        io = tokens * lh * (2 * (2 * ld + lv) + 4 * ld + 4 * lv)
+        roof["gla_prefill_GBps"] = round(io / t / 1e6, 1)
+        roof["gla_prefill_frac_of_hbm"] = round(roof["gla_prefill_GBps"] / pk["hbm_gbs"], 4)
+        roof["gla_prefill_TFLOPs_fp32"] = round(lh * tokens * 2 * 3 * ld * lv / t / 1e9, 1)
+    t = per_call(Z["prefill_kernels_ms"], "linear_attention")
+    if t:
+        io = tokens * zr["heads"] * (2 * (2 * zr["dim"] + zr["vdim"]) + 4 * zr["vdim"])
+        roof["zalunex_linear_attention_prefill_GBps"] = round(io / t / 1e6, 1)
+        roof["zalunex_linear_attention_prefill_frac_of_hbm"] = round(roof["zalunex_linear_attention_prefill_GBps"] / pk["hbm_gbs"], 4)
+    pairs = tokens * 6
+    t = per_call(F["prefill_kernels_ms"], "routed_experts")
+    if t:
+        roof["experts_prefill_TFLOPs"] = round(pairs * 3 * 2 * w * 1408 / t / 1e9, 1)
+        roof["experts_prefill_frac_of_burst"] = round(roof["experts_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    t = per_call(Z["prefill_kernels_ms"], "routed_experts")
+    if t:
+        roof["zalunex_experts_prefill_TFLOPs"] = round(pairs * 2 * 2 * w * 1408 / t / 1e9, 1)
+        roof["zalunex_experts_prefill_frac_of_burst"] = round(roof["zalunex_experts_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    t = F["prefill_kernels_ms"].get("matmul_nt")
+    if t:   # all library products of the prompt: projections in and out of the four mixers, the decays' two, gated units, shared experts, head
+        n_att = 2 * ((H + G) * d + G * vd + H * vd) + H * vd
+        n_lin = 2 * (2 * lh * ld + 3 * lh * lv)
+        flops = 2 * tokens * (w * (n_att + n_lin) + 2 * (64 * w + 64 * lh * ld) + 2 * 3 * w * 4 * w + 2 * 3 * w * 2816)
+        roof["library_products_TFLOPs"] = round(flops / t["ms"] / 1e9, 1)
+        roof["library_products_frac_of_burst"] = round(roof["library_products_TFLOPs"] / pk["bf16_tflops"], 4)
+    for key, bytes_per_row in (("norm_stream", w * (4 + 4 + 4 + 2)), ("head_norm_gate", lh * lv * (4 + 2 + 2)),
+                               ("rope_norm_store", ((H + G) * d + G * vd) * 4), ("gla_decay_", lh * ld * 8)):
+        t = per_call(F["prefill_kernels_ms"], key)
+        if t:
+            roof[f"{key}_prefill_GBps"] = round(tokens * bytes_per_row / t / 1e6, 1)
+            roof[f"{key}_prefill_frac_of_hbm"] = round(roof[f"{key}_prefill_GBps"] / pk["hbm_gbs"], 4)
+    t = F["prefill_kernels_ms"].get("glu_act")
+    if t:   # two gated units of 4 w and two shared experts of 2,816 columns: gate and up in, product out
+        roof["glu_act_prefill_GBps"] = round(tokens * 6 * (2 * 4 * w + 2 * 2816) / t["ms"] / 1e6, 1)
+        roof["glu_act_prefill_frac_of_hbm"] = round(roof["glu_act_prefill_GBps"] / pk["hbm_gbs"], 4)
+    zw = zalunex_config(args.size)["width"]
+    for key, bytes_per_row in (("post_norm_add", zw * (4 + 4 + 4 + 2)), ("norm_gate", zr["heads"] * zr["vdim"] * (4 + 2 + 2)),
+                               ("qk_norm_store", (zl["heads"] + 2 * zl["kv_heads"]) * 128 * 4), ("glu_clamp", 4 * zw * 6)):
+        t = per_call(Z["prefill_kernels_ms"], key)
+        if t:
+            roof[f"zalunex_{key}_prefill_GBps"] = round(tokens * bytes_per_row / t / 1e6, 1)
+            roof[f"zalunex_{key}_prefill_frac_of_hbm"] = round(roof[f"zalunex_{key}_prefill_GBps"] / pk["hbm_gbs"], 4)
+    result["roofline"] = roof
+    result["peaks"] = pk
+    print(json.dumps(result))
+    return 0
+
 
 def run_ours(args):
+    if args.only == "figudra":
+        return run_figudra(args)
     if args.only == "pafevik":
         return run_pafevik(args)
     if args.only == "pogezen":
@@ -1233,10 +1352,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "prefill-attention", "config", "linear",
-                             "fill", "mma-cadence", "pafevik", "zalunex", "pogezen"],
+                             "fill", "mma-cadence", "pafevik", "zalunex", "pogezen", "figudra"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
-    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik, --only zalunex and --only pogezen")
+    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik, --only zalunex, --only pogezen and --only figudra")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
     ap.add_argument("--past", type=int, default=0, help="cached tokens before the prompt for --only prefill-attention")

@@ -105,6 +105,25 @@ CONFIGS = {
 }
 
 
+def steady(cfg):
+    """The configuration with routers that choose every expert (all groups kept, ``top`` = all): the weights still
+    come from the scores, but no choice can fall the other way. A bfloat16 model's stream differs from the plain
+    implementation's by about a hundredth, which moves a token's scores by as much; among six to sixteen scores some
+    pair at the edge of the choice is that close in one token out of ten, the token then runs other experts, and the
+    recurrent layers carry the difference to every later token. Whole models in bfloat16 are compared under these
+    routers; the choice itself is compared in float32 whole models and, in both dtypes, on the parts alone, where
+    the plain implementation reads the same input rows."""
+    import copy
+    cfg = copy.deepcopy(cfg)
+    for layer in cfg["layers"]:
+        mlp = layer.get("mlp")
+        if mlp is not None and mlp["kind"] == "moe":
+            r = mlp["router"]
+            r["top"] = r["experts"]
+            r["groups"] = dict(r.get("groups") or {"count": 1}, keep=(r.get("groups") or {"count": 1})["count"])
+    return cfg
+
+
 def tensor_shapes(cfg):
     W = cfg["width"]
     shapes = {"embed": (cfg["vocab"], W), "embed.norm": (W,), "final.norm": (W,), "head": (cfg["vocab"], W)}
