@@ -7,8 +7,8 @@
 // come as their logarithms (float32 [tokens, heads * dim]); a row of S is updated as S + (expm1(log a) S + k v), so
 // that a decay close to one keeps its digits. All arithmetic on S is float32 whatever the model dtype.
 //
-// One kernel walks tokens in order with S in registers: a block owns VB value columns of one head, warp w the rows
-// [w ROWS, (w + 1) ROWS) of S, lane j column j; a token's q, k and decays are staged in shared memory one token
+// One kernel walks tokens in order with S in registers: a block owns VB or 2 VB value columns of one head, warp w the
+// rows [w ROWS, (w + 1) ROWS) of S, lane j column j (and j + 32); the tokens' q, k and decays are staged in shared memory a batch
 // ahead, and the warps' partial outputs meet there in a fixed order. It runs in three roles: over a sequence's new
 // tokens from and to the state area (steps of any length); over one chunk of 64 tokens from zero, leaving the
 // chunk's own sum and its total decay (pass 1 of the chunked form); over one chunk from the state before it, with
@@ -24,6 +24,10 @@ constexpr int CH = 64;          // tokens of a chunk
 
 enum { GLA_WALK = 0, GLA_CHUNK_SUM = 1, GLA_CHUNK_OUT = 2 };
 
+// tokens of a batch of the walk, by the rows of S a warp owns and the value columns a lane owns (what fits the
+// registers that hold the next batch, and 48 KB of shared memory)
+__host__ __device__ constexpr int walk_batch(int rows, int cols) { return (rows == 32 || cols == 2) ? 8 : 16; }
+
 // z <- logsigmoid(z + bias) / tau: the logarithm of sigmoid(z + bias)^(1 / tau)
 __global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict__ bias, long long total, int width,
                                  float inv_tau) {
@@ -36,17 +40,34 @@ __global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict_
 // proj row t: [q: heads * dim | k: heads * dim | v: heads * v_dim | ...], `stride` elements apart.
 // role GLA_WALK: blockIdx.x = sequence; GLA_CHUNK_*: blockIdx.x = chunk (chunk_seq, chunk_q0 say which tokens).
 // sums [chunks][heads][dim][v_dim]; chunk_decay [chunks][heads][dim]: the sum of the chunk's logarithms of decays.
-template <typename T, int ROWS>
-__global__ void __launch_bounds__(32 * MAX_WARPS)
+//
+// Tokens are staged in batches of SB: while a batch is computed from shared memory, the next one's q, k, decays and
+// values are already on their way into registers (a token's loads alone take longer than its arithmetic), and the
+// warps' partial outputs of a whole batch meet once: two block barriers a batch, none a token. With dim a multiple of
+// 4 a warp reads four neighbouring rows' q, k and decays in one 16-byte word each.
+// DIMC: the number of key channels where the instance is compiled for one (64, 128: the rows' tests and the addresses in
+// shared memory are then constants), 0 for any.
+template <typename T, int ROWS, int COLS, int DIMC>
+__global__ void __launch_bounds__(32 * MAX_WARPS, ROWS == 32 ? 1 : 2)
 gla_walk_kernel(const T* __restrict__ proj, int stride, const float* __restrict__ log_decay, float* __restrict__ state,
                 int state_stride, const int* __restrict__ slots, StepBatch sb, const int* __restrict__ chunk_seq,
                 const int* __restrict__ chunk_q0, float* __restrict__ sums, float* __restrict__ chunk_decay,
-                float* __restrict__ out, int heads, int dim, int v_dim, float q_scale, int role) {
-  __shared__ float qs[2][32 * MAX_WARPS], ks[2][32 * MAX_WARPS], es[2][32 * MAX_WARPS];
-  __shared__ float part[2][MAX_WARPS][VB];
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, warps = blockDim.x / 32;
-  const int h = blockIdx.y, j = blockIdx.z * VB + lane;
-  const bool mine = j < v_dim;
+                float* __restrict__ out, int heads, int dim_any, int v_dim, float q_scale, int role) {
+  const int dim = DIMC > 0 ? DIMC : dim_any;
+  constexpr int SB = walk_batch(ROWS, COLS);   // tokens of a batch
+  constexpr int IT = SB * ROWS / 32;           // (token, channel) pairs a thread stages of each of q, k and the decays
+  constexpr int VBC = VB * COLS;               // value columns of a block: lane l owns columns l, l + 32, ...
+  extern __shared__ __align__(16) float sm[];
+  const int pitch = (dim + 3) & ~3;            // a token's row of channels, at whole 16-byte words
+  float* qs = sm;                              // [SB][pitch]
+  float* ks = qs + SB * pitch;
+  float* es = ks + SB * pitch;
+  float* vs = es + SB * pitch;                 // [SB][VBC]
+  float* part = vs + SB * VBC;                 // [SB][warps][VBC]
+  // every block has 32 * MAX_WARPS threads: warps whose rows lie past dim stage and sum with the others and hold zeros
+  constexpr int nthreads = 32 * MAX_WARPS, warps = MAX_WARPS, RV = SB * VBC / nthreads;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int h = blockIdx.y, j0 = blockIdx.z * VBC;
   int seq, first, n;
   if (role == GLA_WALK) {
     seq = blockIdx.x;
@@ -62,86 +83,168 @@ gla_walk_kernel(const T* __restrict__ proj, int stride, const float* __restrict_
   float* st = nullptr;
   if (role == GLA_WALK) st = state + size_t(slots[seq]) * state_stride + size_t(h) * per_head;
   else st = sums + (size_t(blockIdx.x) * heads + h) * per_head;
-  float S[ROWS];
+  float S[ROWS][COLS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     const int d = warp * ROWS + r;
-    S[r] = (role != GLA_CHUNK_SUM && mine && d < dim) ? st[size_t(d) * v_dim + j] : 0.f;
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) {
+      const int j = j0 + c * 32 + lane;
+      S[r][c] = (role != GLA_CHUNK_SUM && j < v_dim && d < dim) ? st[size_t(d) * v_dim + j] : 0.f;
+    }
   }
   const int k_off = heads * dim, v_off = 2 * heads * dim;
-  const int sd = threadIdx.x;            // the channel this thread stages
-  const bool stages = sd < dim;
-  float total_log = 0.f;
-  // token 0 is staged before the loop, token i + 1 while token i is computed
-  float nq = 0.f, nk = 0.f, ne = 0.f, nv = 0.f;
-  if (n > 0) {
-    const T* row = proj + size_t(first) * stride;
-    if (stages) {
-      nq = to_f(row[h * dim + sd]) * q_scale;
-      nk = to_f(row[k_off + h * dim + sd]);
-      const float la = log_decay[size_t(first) * k_off + h * dim + sd];
-      total_log += la;
-      ne = expm1f(la);
-    }
-    if (mine) nv = to_f(row[v_off + h * v_dim + j]);
-    if (stages) {
-      qs[0][sd] = nq;
-      ks[0][sd] = nk;
-      es[0][sd] = ne;
-    }
-  }
-  for (int i = 0; i < n; ++i) {
-    const int b = i & 1;
-    const float v = nv;
-    __syncthreads();      // token i is staged; the partial outputs of token i - 1 are written
-    if (i + 1 < n) {      // the next token's loads are issued now and stored after this token's arithmetic
-      const T* row = proj + size_t(first + i + 1) * stride;
-      if (stages) {
-        nq = to_f(row[h * dim + sd]) * q_scale;
-        nk = to_f(row[k_off + h * dim + sd]);
-        ne = log_decay[size_t(first + i + 1) * k_off + h * dim + sd];
-      }
-      if (mine) nv = to_f(row[v_off + h * v_dim + j]);
-    }
-    if (role != GLA_CHUNK_SUM && i > 0 && warp == 0 && mine) {
-      float o = 0.f;
-      for (int w = 0; w < warps; ++w) o += part[b ^ 1][w][lane];
-      out[(size_t(first + i - 1) * heads + h) * v_dim + j] = o;
-    }
-    float o = 0.f;
+  const bool with_out = role != GLA_CHUNK_SUM;
+  const bool vec = (dim & 3) == 0;
+  // staged values stay as they were loaded (no arithmetic that would wait for a load between two loads)
+  T rq[IT], rk[IT], rv[RV];
+  float re[IT];
+  // the (token, channel) pairs this thread stages: pair it is tid + it * nthreads, walked without divisions
+  const int t_first = tid / dim, d_first = tid - t_first * dim, t_step = nthreads / dim, d_step = nthreads - t_step * dim;
+
+  // the loads of the batch that starts at token t0 (nb tokens), into registers
+  auto fetch = [&](int t0, int nb) {
+    int t = t_first, d = d_first;
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      const int d = warp * ROWS + r;       // rows past dim hold zeros and read staged zeros or stale values times zero
-      if (d < dim) {
-        S[r] = S[r] + fmaf(es[b][d], S[r], ks[b][d] * v);
-        o = fmaf(S[r], qs[b][d], o);
+    for (int it = 0; it < IT; ++it) {
+      const int tt = min(t, nb - 1);      // a pair past the batch reads the batch's last token and is not stored
+      const T* row = proj + size_t(first + t0 + tt) * stride + h * dim + d;
+      rq[it] = row[0];
+      rk[it] = row[k_off];
+      re[it] = log_decay[size_t(first + t0 + tt) * k_off + h * dim + d];
+      t += t_step;
+      d += d_step;
+      if (d >= dim) {
+        d -= dim;
+        ++t;
       }
     }
-    if (role != GLA_CHUNK_SUM) part[b][warp][lane] = o;
-    if (i + 1 < n && stages) {
-      total_log += ne;
-      qs[b ^ 1][sd] = nq;
-      ks[b ^ 1][sd] = nk;
-      es[b ^ 1][sd] = expm1f(ne);
+#pragma unroll
+    for (int it = 0; it < RV; ++it) {
+      const int idx = tid + it * nthreads;       // (token, column): idx / VBC, idx % VBC
+      const int tt = min(idx / VBC, nb - 1), col = min(j0 + (idx % VBC), v_dim - 1);
+      rv[it] = proj[size_t(first + t0 + tt) * stride + v_off + h * v_dim + col];
     }
-  }
-  if (role != GLA_CHUNK_SUM && n > 0) {
-    __syncthreads();
-    if (warp == 0 && mine) {
-      float o = 0.f;
-      for (int w = 0; w < warps; ++w) o += part[(n - 1) & 1][w][lane];
-      out[(size_t(first + n - 1) * heads + h) * v_dim + j] = o;
+  };
+  auto store = [&](int nb) {
+    int t = t_first, d = d_first;
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      if (t < nb) {
+        qs[t * pitch + d] = to_f(rq[it]) * q_scale;
+        ks[t * pitch + d] = to_f(rk[it]);
+        es[t * pitch + d] = expm1f(re[it]);
+      }
+      t += t_step;
+      d += d_step;
+      if (d >= dim) {
+        d -= dim;
+        ++t;
+      }
     }
+#pragma unroll
+    for (int it = 0; it < RV; ++it) {
+      const int idx = tid + it * nthreads;
+      if (idx < nb * VBC) vs[idx] = (j0 + (idx % VBC) < v_dim) ? to_f(rv[it]) : 0.f;
+    }
+  };
+
+  if (n > 0) fetch(0, min(SB, n));
+  for (int t0 = 0; t0 < n; t0 += SB) {
+    const int nb = min(SB, n - t0);
+    store(nb);
+    __syncthreads();                                   // the batch is staged
+    if (t0 + SB < n) fetch(t0 + SB, min(SB, n - t0 - SB));   // the next batch's loads run under this batch's arithmetic
+    // unrolled over the batch's tokens: the next token's reads of shared memory are issued under this token's arithmetic
+    // (the partial outputs are kept in registers until the batch's end, so no store stands between two tokens' reads)
+    float ob[SB][COLS];
+#pragma unroll
+    for (int t = 0; t < SB; ++t) {
+      if (t >= nb) break;
+      float v[COLS], o[COLS];
+#pragma unroll
+      for (int c = 0; c < COLS; ++c) {
+        v[c] = vs[t * VBC + c * 32 + lane];
+        o[c] = 0.f;
+      }
+      const float* qr = qs + t * pitch + warp * ROWS;
+      const float* kr = ks + t * pitch + warp * ROWS;
+      const float* er = es + t * pitch + warp * ROWS;
+      // a row's update: S + expm1(log a) S, then + k v: two fused multiply-adds
+      if (vec) {
+#pragma unroll
+        for (int r = 0; r < ROWS; r += 4) {
+          if (warp * ROWS + r < dim) {        // whole quads: dim and ROWS are multiples of 4
+            const float4 e4 = *reinterpret_cast<const float4*>(er + r);
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + r);
+            const float4 q4 = with_out ? *reinterpret_cast<const float4*>(qr + r) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int c = 0; c < COLS; ++c) {
+              S[r][c] = fmaf(k4.x, v[c], fmaf(e4.x, S[r][c], S[r][c]));
+              S[r + 1][c] = fmaf(k4.y, v[c], fmaf(e4.y, S[r + 1][c], S[r + 1][c]));
+              S[r + 2][c] = fmaf(k4.z, v[c], fmaf(e4.z, S[r + 2][c], S[r + 2][c]));
+              S[r + 3][c] = fmaf(k4.w, v[c], fmaf(e4.w, S[r + 3][c], S[r + 3][c]));
+              if (with_out) o[c] = fmaf(S[r + 3][c], q4.w, fmaf(S[r + 2][c], q4.z, fmaf(S[r + 1][c], q4.y, fmaf(S[r][c], q4.x, o[c]))));
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          if (warp * ROWS + r < dim) {
+#pragma unroll
+            for (int c = 0; c < COLS; ++c) {
+              S[r][c] = fmaf(kr[r], v[c], fmaf(er[r], S[r][c], S[r][c]));
+              if (with_out) o[c] = fmaf(S[r][c], qr[r], o[c]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < COLS; ++c) ob[t][c] = o[c];
+    }
+    if (with_out) {
+#pragma unroll
+      for (int t = 0; t < SB; ++t) {
+        if (t < nb) {
+#pragma unroll
+          for (int c = 0; c < COLS; ++c) part[(t * warps + warp) * VBC + c * 32 + lane] = ob[t][c];
+        }
+      }
+    }
+    __syncthreads();                                   // the batch's partial outputs are written; its rows are no longer read
+    if (with_out) {
+      for (int idx = tid; idx < nb * VBC; idx += nthreads) {
+        const int t = idx / VBC, l = idx % VBC;
+        if (j0 + l < v_dim) {
+          float o = 0.f;
+          for (int w = 0; w < warps; ++w) o += part[(t * warps + w) * VBC + l];     // a fixed order
+          out[(size_t(first + t0 + t) * heads + h) * v_dim + j0 + l] = o;
+        }
+      }
+    }
+    // the next store writes rows that were last read before the barrier above; `part` is written again only after the
+    // next batch's first barrier, which every thread reaches after this sum
   }
-  if (role != GLA_CHUNK_OUT && mine) {
+  if (role != GLA_CHUNK_OUT) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       const int d = warp * ROWS + r;
-      if (d < dim) st[size_t(d) * v_dim + j] = S[r];
+#pragma unroll
+      for (int c = 0; c < COLS; ++c) {
+        const int j = j0 + c * 32 + lane;
+        if (d < dim && j < v_dim) st[size_t(d) * v_dim + j] = S[r][c];
+      }
     }
   }
-  if (role == GLA_CHUNK_SUM && blockIdx.z == 0 && stages)
-    chunk_decay[(size_t(blockIdx.x) * heads + h) * dim + sd] = total_log;
+  if (role == GLA_CHUNK_SUM && blockIdx.z == 0) {
+    for (int d = tid; d < dim; d += nthreads) {        // the chunk's total decay per channel, tokens in order
+      float total = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < n; ++i) total += log_decay[size_t(first + i) * k_off + h * dim + d];
+      chunk_decay[(size_t(blockIdx.x) * heads + h) * dim + d] = total;
+    }
+  }
 }
 
 // One thread per (sequence, head, element of S): walks the sequence's chunks in order; sums[c] becomes the state
@@ -182,15 +285,29 @@ int launch_walk(const void* proj, int stride, const float* log_decay, float* sta
                 const StepBatch& sb, const int* chunk_seq, const int* chunk_q0, int n_blocks, float* sums, float* chunk_decay,
                 float* out, int heads, int dim, int v_dim, float q_scale, int role, cudaStream_t stream) {
   const int rows = dim <= 8 * MAX_WARPS ? 8 : (dim <= 16 * MAX_WARPS ? 16 : 32);
-  const int warps = (dim + rows - 1) / rows;
-  dim3 grid(n_blocks, heads, (v_dim + VB - 1) / VB);
-#define PTB_GLA(ROWS)                                                                                                  \
-  gla_walk_kernel<T, ROWS><<<grid, 32 * warps, 0, stream>>>((const T*)proj, stride, log_decay, state, state_stride, slots, \
-                                                            sb, chunk_seq, chunk_q0, sums, chunk_decay, out, heads, dim,   \
-                                                            v_dim, q_scale, role)
-  if (rows == 8) PTB_GLA(8);
-  else if (rows == 16) PTB_GLA(16);
-  else PTB_GLA(32);
+  const int warps = MAX_WARPS;
+  const int cols = v_dim > VB ? 2 : 1;       // two value columns a lane where a head's values are wider than a warp
+  dim3 grid(n_blocks, heads, (v_dim + VB * cols - 1) / (VB * cols));
+  const int batch = walk_batch(rows, cols), pitch = (dim + 3) & ~3;
+  const size_t smem = sizeof(float) * (size_t(3) * batch * pitch + size_t(batch) * VB * cols + size_t(batch) * warps * VB * cols);
+#define PTB_GLA(ROWS, COLS, DIMC)                                                                                        \
+  gla_walk_kernel<T, ROWS, COLS, DIMC><<<grid, 32 * warps, smem, stream>>>((const T*)proj, stride, log_decay, state,      \
+                                                                           state_stride, slots, sb, chunk_seq, chunk_q0,  \
+                                                                           sums, chunk_decay, out, heads, dim, v_dim,     \
+                                                                           q_scale, role)
+  if (cols == 1) {
+    if (dim == 64) PTB_GLA(8, 1, 64);
+    else if (dim == 128) PTB_GLA(16, 1, 128);
+    else if (rows == 8) PTB_GLA(8, 1, 0);
+    else if (rows == 16) PTB_GLA(16, 1, 0);
+    else PTB_GLA(32, 1, 0);
+  } else {
+    if (dim == 64) PTB_GLA(8, 2, 64);
+    else if (dim == 128) PTB_GLA(16, 2, 128);
+    else if (rows == 8) PTB_GLA(8, 2, 0);
+    else if (rows == 16) PTB_GLA(16, 2, 0);
+    else PTB_GLA(32, 2, 0);
+  }
 #undef PTB_GLA
   return launch_status();
 }
