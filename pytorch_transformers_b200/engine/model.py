@@ -377,6 +377,7 @@ class CausalLM:
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(device=self.device)
             ctx.side_stream = self._side_stream
+        normed = False      # has the norm of the embeddings been applied already?
         if self.position_table is not None:
             # embeddings plus the positions' learned vectors, straight into the float32 stream
             x = k.embed_sum(ctx.dev["tokens"], ctx.dev["tok_pos"], self.embedding, self.position_table, self.status)
@@ -385,11 +386,12 @@ class CausalLM:
             x = k.embed_rows(ctx.dev["tokens"], self.embedding, self.spec.embedding_scale, self.status)
             if self.embedding_norm is not None:     # normed in float32, never rounded
                 x = self.embedding_norm.forward_same(x)
+                normed = True
         else:
             x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
             if self.spec.embedding_scale != 1.0:
                 k.scale_(x, self.spec.embedding_scale)
-        if self.embedding_norm is not None and x.dtype != torch.float32:
+        if self.embedding_norm is not None and not normed:
             x = self.embedding_norm.forward(x)
         if self.spec.stream_float32 and x.dtype != torch.float32:
             x = k.to_float(x)       # from here to the final norm the stream is float32
