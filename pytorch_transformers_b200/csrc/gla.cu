@@ -28,6 +28,20 @@ enum { GLA_WALK = 0, GLA_CHUNK_SUM = 1, GLA_CHUNK_OUT = 2 };
 // registers that hold the next batch, and 48 KB of shared memory)
 __host__ __device__ constexpr int walk_batch(int rows, int cols) { return (rows == 32 || cols == 2) ? 8 : 16; }
 
+// Two float32 lanes in one 64-bit register and their fused multiply-add in one instruction (each lane rounds as fmaf does).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 // z <- logsigmoid(z + bias) / tau: the logarithm of sigmoid(z + bias)^(1 / tau)
 __global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict__ bias, long long total, int width,
                                  float inv_tau) {
@@ -83,14 +97,29 @@ gla_walk_kernel(const T* __restrict__ proj, int stride, const float* __restrict_
   float* st = nullptr;
   if (role == GLA_WALK) st = state + size_t(slots[seq]) * state_stride + size_t(h) * per_head;
   else st = sums + (size_t(blockIdx.x) * heads + h) * per_head;
-  float S[ROWS][COLS];
+  // Where the key size is compiled in, two neighbouring rows of a column share a 64-bit register and every update of
+  // the pair is one instruction: half as many to issue. The outputs then sum even and odd rows apart.
+  constexpr bool PACK = DIMC > 0;
+  float S[PACK ? 1 : ROWS][COLS];
+  f32x2 S2[PACK ? ROWS / 2 : 1][COLS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     const int d = warp * ROWS + r;
 #pragma unroll
     for (int c = 0; c < COLS; ++c) {
       const int j = j0 + c * 32 + lane;
-      S[r][c] = (role != GLA_CHUNK_SUM && j < v_dim && d < dim) ? st[size_t(d) * v_dim + j] : 0.f;
+      const float s0 = (role != GLA_CHUNK_SUM && j < v_dim && d < dim) ? st[size_t(d) * v_dim + j] : 0.f;
+      if constexpr (PACK) {
+        if (r & 1) {
+          float lo, hi;
+          unpack2(S2[r / 2][c], lo, hi);
+          S2[r / 2][c] = pack2(lo, s0);
+        } else {
+          S2[r / 2][c] = pack2(s0, 0.f);
+        }
+      } else {
+        S[r][c] = s0;
+      }
     }
   }
   const int k_off = heads * dim, v_off = 2 * heads * dim;
@@ -171,7 +200,34 @@ gla_walk_kernel(const T* __restrict__ proj, int stride, const float* __restrict_
       const float* kr = ks + t * pitch + warp * ROWS;
       const float* er = es + t * pitch + warp * ROWS;
       // a row's update: S + expm1(log a) S, then + k v: two fused multiply-adds
-      if (vec) {
+      if constexpr (PACK) {
+        f32x2 vv[COLS], o2[COLS];
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+          vv[c] = pack2(v[c], v[c]);
+          o2[c] = pack2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; r += 4) {
+          const float4 e4 = *reinterpret_cast<const float4*>(er + r);
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + r);
+          const float4 q4 = with_out ? *reinterpret_cast<const float4*>(qr + r) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const f32x2 e01 = pack2(e4.x, e4.y), e23 = pack2(e4.z, e4.w), k01 = pack2(k4.x, k4.y), k23 = pack2(k4.z, k4.w);
+          const f32x2 q01 = pack2(q4.x, q4.y), q23 = pack2(q4.z, q4.w);
+#pragma unroll
+          for (int c = 0; c < COLS; ++c) {
+            S2[r / 2][c] = fma2(k01, vv[c], fma2(e01, S2[r / 2][c], S2[r / 2][c]));
+            S2[r / 2 + 1][c] = fma2(k23, vv[c], fma2(e23, S2[r / 2 + 1][c], S2[r / 2 + 1][c]));
+            if (with_out) o2[c] = fma2(S2[r / 2 + 1][c], q23, fma2(S2[r / 2][c], q01, o2[c]));
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+          float lo, hi;
+          unpack2(o2[c], lo, hi);
+          o[c] = lo + hi;
+        }
+      } else if (vec) {
 #pragma unroll
         for (int r = 0; r < ROWS; r += 4) {
           if (warp * ROWS + r < dim) {        // whole quads: dim and ROWS are multiples of 4
@@ -233,7 +289,15 @@ gla_walk_kernel(const T* __restrict__ proj, int stride, const float* __restrict_
 #pragma unroll
       for (int c = 0; c < COLS; ++c) {
         const int j = j0 + c * 32 + lane;
-        if (d < dim && j < v_dim) st[size_t(d) * v_dim + j] = S[r][c];
+        float s1;
+        if constexpr (PACK) {
+          float lo, hi;
+          unpack2(S2[r / 2][c], lo, hi);
+          s1 = (r & 1) ? hi : lo;
+        } else {
+          s1 = S[r][c];
+        }
+        if (d < dim && j < v_dim) st[size_t(d) * v_dim + j] = s1;
       }
     }
   }
