@@ -25,6 +25,11 @@ from .pafevik import _positive_int
 MIXERS = ("gla", "attention", "attention_2")
 
 
+def _whole(v: Any) -> bool:
+    """An integer, also one that JSON wrote as 64.0."""
+    return (isinstance(v, int) and not isinstance(v, bool)) or (isinstance(v, float) and v.is_integer())
+
+
 def _check_mixer(kind: str, m: Dict[str, Any], where: str) -> None:
     _require(isinstance(m, dict), f"{where}.mixer must be an object")
     for key in ("heads", "dim", "vdim"):
@@ -39,18 +44,18 @@ def _check_mixer(kind: str, m: Dict[str, Any], where: str) -> None:
         _require(float(m.get("softcap") or 0) >= 0, f"{where}.mixer.softcap must not be negative")
         temp = m.get("q_temp")
         if temp is not None:
-            _require(isinstance(temp, dict) and isinstance(temp.get("every"), int) and temp["every"] > 0
+            _require(isinstance(temp, dict) and _whole(temp.get("every")) and temp["every"] > 0
                      and isinstance(temp.get("coef"), (int, float)),
                      f"{where}.mixer.q_temp must give a number coef and a positive integer every")
         return
     mask = m.get("mask") or {}
     _require(isinstance(mask, dict), f"{where}.mixer.mask must be an object")
     size, keep = mask.get("size", 0), mask.get("keep_first", 0)
-    _require(isinstance(size, int) and size >= 0 and isinstance(keep, int) and keep >= 0,
+    _require(_whole(size) and size >= 0 and _whole(keep) and keep >= 0,
              f"{where}.mixer.mask.size and keep_first must be integers >= 0")
     rot = m.get("rot") or {}
     dims = rot.get("dims", 0)
-    _require(isinstance(dims, int) and 0 <= dims <= m["dim"] and dims % 2 == 0,
+    _require(_whole(dims) and 0 <= dims <= m["dim"] and dims % 2 == 0,
              f"{where}.mixer.rot.dims must be even and at most dim")
     _require(dims == 0 or float(rot.get("base", 0)) > 0, f"{where}.mixer.rot.base must be positive")
     sc = rot.get("scaling")
@@ -109,8 +114,8 @@ class FigudraConfig(ModelConfig):
                 _require(isinstance(j, int) and not isinstance(j, bool) and 0 <= j < len(self.layers) and j != i
                          and isinstance(self.layers[j], dict) and self.layers[j].get("weights_of") is None,
                          f"{where}.weights_of must name another layer that has weights of its own, got {j!r}")
-                own = {k: v for k, v in layer.items() if k != "weights_of"}
-                _require(own == self.layers[j], f"{where} uses the weights of layer {j} and must equal it otherwise")
+                same = all(layer.get(k) == self.layers[j].get(k) for k in ("type", "mixer", "mlp"))
+                _require(same, f"{where} uses the weights of layer {j} and must equal it in type, mixer and mlp")
 
     def weights_layer(self, i: int) -> int:
         """The layer whose tensors layer ``i`` runs."""

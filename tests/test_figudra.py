@@ -106,6 +106,23 @@ def test_configurations_that_cannot_be_built_are_refused(bad):
         ptb.FigudraConfig.from_dict(_with("mixed", **bad))
 
 
+def test_keys_that_the_design_does_not_know_and_whole_numbers_written_as_floats_are_taken():
+    """A configuration file may carry notes of its writer (a seed, a name), say ``weights_of: null`` for a layer with
+    weights of its own and write a count as 16.0; the model is the same."""
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200.models.figudra import figudra_spec
+    plain_cfg = ptb.FigudraConfig.from_dict(_with("mixed"))
+    temp = {"coef": 0.7, "every": 16.0}        # layer 5 runs layer 0's weights: their mixers stay equal
+    noted = _with("mixed", seed=11, layers__1__weights_of=None, layers__0__note="first", layers__4__mixer__comment="x",
+                  layers__0__mixer__q_temp=temp, layers__5__mixer__q_temp=temp,
+                  layers__2__mixer__mask={"size": 33.0, "keep_first": 5.0}, layers__2__mixer__rot__dims=8.0)
+    cfg = ptb.FigudraConfig.from_dict(noted)
+    assert [cfg.weights_layer(i) for i in range(6)] == [plain_cfg.weights_layer(i) for i in range(6)]
+    a, b = figudra_spec(cfg), figudra_spec(plain_cfg)
+    assert [blk.children["mixer"].params for blk in a.blocks] == [blk.children["mixer"].params for blk in b.blocks]
+    assert [(e.block, e.cache_entry) for e in a.schedule] == [(e.block, e.cache_entry) for e in b.schedule]
+
+
 def test_parts_refuse_what_their_kernels_do_not_take():
     from pytorch_transformers_b200 import kernels
     from pytorch_transformers_b200.parts.base import BuildContext, PartSpec, make_part
