@@ -13,7 +13,8 @@
 // tokens from and to the state area (steps of any length); over one chunk of 64 tokens from zero, leaving the
 // chunk's own sum and its total decay (pass 1 of the chunked form); over one chunk from the state before it, with
 // outputs (pass 3). Pass 2 joins the chunks of a sequence in order. The chunked form differs from the plain walk by
-// the order of float32 operations only.
+// the order of float32 operations only. With bfloat16 projections and keys and values of 64 or 128 entries pass 1 is a
+// product on the tensor cores instead (csrc/gla_mma.cu: the decayed keys enter it as two bfloat16 terms).
 #include "common.cuh"
 
 namespace {
@@ -378,6 +379,12 @@ int launch_walk(const void* proj, int stride, const float* log_decay, float* sta
 
 }  // namespace
 
+// pass 1 on the tensor cores (csrc/gla_mma.cu)
+PTB_API int ptb_gla_chunk_sum_mma_supports(int dtype, const void* proj, int stride, const float* log_decay, int dim, int v_dim);
+PTB_API int ptb_gla_chunk_sum_mma(const void* proj, int stride, const float* log_decay, const StepBatch* sb, const int* chunk_seq,
+                                  const int* chunk_q0, int n_chunks, float* sums, float* chunk_decay, int heads, int dim,
+                                  int v_dim, cudaStream_t stream);
+
 PTB_API int ptb_gla_max_dim() { return 32 * MAX_WARPS; }
 PTB_API int ptb_gla_chunk_tokens() { return CH; }
 
@@ -416,9 +423,14 @@ PTB_API int ptb_gla_chunks(int dtype, const void* proj, int stride, const float*
   if (heads <= 0 || heads > 65535 || dim <= 0 || dim > 32 * MAX_WARPS || v_dim <= 0 || stride < 2 * heads * dim + heads * v_dim ||
       sb->n_seqs > 65535)
     return PTB_ERR_SIZE;
+  // a chunk's own sum is a product of the decayed keys by the values: on the tensor cores where the sizes allow
+  const bool sum_mma = ptb_gla_chunk_sum_mma_supports(dtype, proj, stride, log_decay, dim, v_dim) != 0;
   for (int role = GLA_CHUNK_SUM; role <= GLA_CHUNK_OUT; ++role) {
     int rc;
-    if (dtype == PTB_F32)
+    if (role == GLA_CHUNK_SUM && sum_mma)
+      rc = ptb_gla_chunk_sum_mma(proj, stride, log_decay, sb, chunk_seq, chunk_q0, n_chunks, sums, chunk_decay, heads, dim, v_dim,
+                                 stream);
+    else if (dtype == PTB_F32)
       rc = launch_walk<float>(proj, stride, log_decay, state, state_stride, slots, *sb, chunk_seq, chunk_q0, n_chunks, sums,
                               chunk_decay, out, heads, dim, v_dim, q_scale, role, stream);
     else if (dtype == PTB_BF16)

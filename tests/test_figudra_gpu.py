@@ -258,6 +258,50 @@ def test_a_far_key_on_an_open_channel_and_on_a_closed_one(n, back):
         assert (last[1] - faded * v[at, 1].double()).norm() < 0.05 * 25.0 * v[at, 1].double().norm() + 1.0
 
 
+@pytest.mark.parametrize("d,vd", [(64, 64), (64, 128), (128, 64), (128, 128)])
+def test_chunk_sums_on_the_tensor_cores(d, vd):
+    """Kernel alone, bfloat16 projections with keys and values of 64 or 128 entries: a chunk's own sum is a product on the
+    tensor cores whose float32 operand (the decayed keys) is split in two. Two sequences side by side with a short last
+    chunk each; channels that stay open, that fade slowly and that close within a few tokens; compared with the plain
+    recurrence on the same rounded projections far below bfloat16's rounding."""
+    from pytorch_transformers_b200.cache.paged import Cache
+    from pytorch_transformers_b200.engine.batch import StepContext
+    from pytorch_transformers_b200.parts.base import StateNeed
+    from pytorch_transformers_b200.parts.recurrent import RecurrenceChunks
+    k = K()
+    H, lengths = 3, [300, 449]
+    g = torch.Generator().manual_seed(d + vd)
+    n = sum(lengths)
+    q, kk, v = (bf16_exact(torch.randn(n, H, x, generator=g)).float() for x in (d, d, vd))
+    la = -torch.rand(n, H, d, generator=g) * 0.2
+    la[:, :, 0] = 0.0                   # never decays
+    la[:, :, 1] = -6.0                  # all but gone after one token
+    la[:, 1, 2::3] *= 40.0              # a head with many fast channels
+    proj = torch.cat([q.reshape(n, -1), kk.reshape(n, -1), v.reshape(n, -1)], 1).bfloat16().cuda()
+    refs, lo = [], 0
+    for L in lengths:
+        refs.append(plain.gla_recurrence(q[lo:lo + L].double() * d ** -0.5, kk[lo:lo + L].double(), v[lo:lo + L].double(),
+                                         la[lo:lo + L].double().exp()))
+        lo += L
+    cache = Cache([(0, None, StateNeed(H * d * vd))], 1024, torch.bfloat16, "cuda", max_slots=len(lengths))
+    slots = [cache.open() for _ in lengths]
+    ctx = StepContext(cache, slots, [[0] * L for L in lengths], 1, [[]] * len(lengths), [RecurrenceChunks()])
+    plan = ctx.plan(RecurrenceChunks.plan_key)
+    assert plan.facts["n_chunks"] == sum((L + 63) // 64 for L in lengths)
+    chunks = (plan.dev["chunk_seq"], plan.dev["chunk_q0"], plan.dev["seq_chunk0"], plan.facts["n_chunks"])
+    entry = type("E", (), {"cache_entry": 0, "state_offset": 0})()
+    state = ctx.state_of(entry, H * d * vd)
+    got = k.gla(proj, la.reshape(n, -1).cuda().contiguous(), state, ctx.dev["slots"], ctx.batch_c[0], H, d, vd, d ** -0.5, chunks)
+    walked = k.gla(proj, la.reshape(n, -1).cuda().contiguous(), torch.zeros_like(state), ctx.dev["slots"], ctx.batch_c[0], H, d,
+                   vd, d ** -0.5, None)
+    ref = torch.cat([r[0].reshape(-1, H * vd) for r in refs])
+    assert row_errors(got, ref).max() < 1e-4, row_errors(got, ref).max()
+    assert row_errors(walked, ref).max() < 2e-5
+    for i, slot in enumerate(slots):        # the state after the last chunk
+        left = state[slot].double().cpu().reshape(H, d, vd)
+        assert (left - refs[i][1]).norm() < 1e-5 * refs[i][1].norm()
+
+
 # ------------------------------------------------------------------------------------------------ the attentions
 def capped_spec(m, width, p="mix."):
     from pytorch_transformers_b200.parts.base import PartSpec
