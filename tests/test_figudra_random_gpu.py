@@ -44,16 +44,16 @@ def random_layer(r: random.Random, kind: str):
     d, vd = r.choice([(8, 8), (12, 20), (24, 12), (40, 40), (64, 64), (64, 32), (128, 128), (96, 48), (128, 64), (32, 32)])
     kv = r.choice([1, 2, 3])
     heads = kv * r.choice([1, 2, 4])
-    scale = r.choice([d ** -0.5, 1.0 / d, 0.3, 0.1875])
+    scale = r.choice([d ** -0.5, 1.0 / d, 0.3, 0.15])
     if kind == "attention":
         return fm.att(heads, kv, d, vd, scale, softcap=r.choice([None, 1.5, 30.0, 50.0]),
-                      q_temp=r.choice([None, (0.5, 64), (1.3, 1), (0.1, 7), (0.25, 100)])), random_mlp(r)
+                      q_temp=r.choice([None, (0.4, 32), (1.3, 1), (0.1, 7), (0.25, 100)])), random_mlp(r)
     rot = None
     if r.random() < 0.85:
         dims = r.choice([2, d // 2 // 2 * 2, d])
-        rot = (dims, r.choice([50.0, 10000.0, 250000.0])) + r.choice([(), (2.0,), (8.0,), (1.0,)])
-    window = r.choice([0, 1, 2, 9, 31, 64, 65, 100, 128, 136, 500])
-    return fm.att2(heads, kv, d, vd, scale, window, r.choice([0, 1, 3, 6, 8, 64, 70]) if window else 0, rot=rot), random_mlp(r)
+        rot = (dims, r.choice([50.0, 10000.0, 1e6])) + r.choice([(), (2.0,), (8.0,), (1.0,)])
+    window = r.choice([0, 1, 2, 9, 31, 64, 65, 100, 128, 140, 500])
+    return fm.att2(heads, kv, d, vd, scale, window, r.choice([0, 1, 3, 5, 8, 64, 70]) if window else 0, rot=rot), random_mlp(r)
 
 
 KINDS = ["gla", "attention", "attention_2"]
