@@ -791,6 +791,32 @@ def test_a_checkpoint_gives_the_decay_rank_that_the_configuration_leaves_out(tmp
     close(model.step(cache, [cache.open()], [ids], want="all"), want, "float32", "rank from the tensor")
 
 
+def test_greedy_generation_from_the_command_line(tmp_path):
+    """The library's command line on a Figudra folder, as a child process: the design is found by the folder's
+    configuration, and the tokens are the plain implementation's."""
+    cfg = fm.CONFIGS["odd"]
+    folder = fm.write_folder(tmp_path, "odd", seed=6)
+    w = fm.torch_weights(cfg, 6)
+    prompts = fm.prompts(cfg, (7, 20), seed=9)
+    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "ptb200-cli")
+    args = [sys.executable, script, "run-generation", "--model_name_or_path", folder, "--fp32", "--greedy", "--length", "8"]
+    for q in prompts:
+        args += ["--prompt_ids", ",".join(map(str, q))]
+    done = subprocess.run(args, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    recs = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    assert [r["prompt_ids"] for r in recs] == prompts
+    for q, r in zip(prompts, recs):
+        ids = list(q)
+        assert len(r["generated_ids"]) == 8
+        for tok in r["generated_ids"]:
+            logits = plain.forward(cfg, w, ids)[-1]
+            top2 = logits.topk(2).values
+            if float(top2[0] - top2[1]) > 1e-4:          # no test on a tie within float32 rounding
+                assert int(logits.argmax()) == tok
+            ids.append(tok)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_trace_runner_as_a_child_process(tmp_path, dtype):
     name = "mixed"
